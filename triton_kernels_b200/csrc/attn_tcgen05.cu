@@ -1,0 +1,356 @@
+// Non-causal flash attention forward for head_dim 128, bf16, on tcgen05 + TMEM.
+//
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and walks the keys in
+// tiles of 128.  Roles (320 threads):
+//   warps 0-3   softmax group 0: thread r owns query row r of tile 0
+//   warps 4-7   softmax group 1: same for tile 1
+//   warp  8     TMA producer: Q once, then K_j, V_j through a 4-slot ring of 32 KB tiles
+//   warp  9     MMA issuer (one thread): S_t = Q_t K_j^T and O_t += P_t V_j
+// TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  P_t (bf16) is written back
+// over the first 64 columns of S_t by the softmax threads and fed to the second MMA straight
+// from TMEM, so probabilities never touch shared memory.  While group 0 does softmax on S_0 the
+// tensor core works on tile 1 and vice versa.
+// Softmax is the usual online form in base 2 with lazy rescaling: the running maximum used for
+// the exponent only moves when a row maximum exceeds it by more than 8 (factor 256), which
+// makes reading and rewriting O in TMEM rare.  Key tails are masked with -inf, query tails are
+// not stored.  Every barrier wait is bounded.
+#include "common.cuh"
+
+namespace fluxb {
+namespace attn {
+
+constexpr int D = 128;
+constexpr int BQ = 128;             // rows per query tile
+constexpr int BKV = 128;            // keys per tile
+constexpr int HALF_BYTES = 128 * 128;  // [128 rows][64 bf16] swizzled block
+constexpr int TILE_BYTES = 2 * HALF_BYTES;
+constexpr int KV_SLOTS = 4;
+constexpr int THREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_SLOTS * TILE_BYTES + 1024 + 256;
+constexpr float kRescaleThreshold = 8.0f;
+
+struct Params {
+  __nv_bfloat16* o;
+  int64_t o_sb, o_sh, o_sl;
+  int Lq, Lk;
+  float scale_log2;
+  uint32_t v_lbo, v_sbo;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+            const __grid_constant__ CUtensorMap tm_v, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* kv_smem = smem + 2 * TILE_BYTES;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(kv_smem + KV_SLOTS * TILE_BYTES);
+  uint64_t* kv_full = q_full + 1;
+  uint64_t* kv_empty = kv_full + KV_SLOTS;
+  uint64_t* s_full = kv_empty + KV_SLOTS;  // [2]
+  uint64_t* p_full = s_full + 2;           // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * (2 * BQ);
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int n_kv = (p.Lk + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_SLOTS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      for (int t = 0; t < 2; ++t)
+        for (int hf = 0; hf < 2; ++hf)
+          tma_load_4d(q_smem + t * TILE_BYTES + hf * HALF_BYTES, &tm_q, q_full, hf * 64, q0 + t * BQ,
+                      head, batch);
+      bool ok = true;
+      for (int i = 0; ok && i < 2 * n_kv; ++i) {  // i even: K_{i/2}, i odd: V_{i/2}
+        const int slot = i % KV_SLOTS;
+        const uint32_t phase = (i / KV_SLOTS) & 1;
+        if (!mbar_wait(&kv_empty[slot], phase ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
+        uint8_t* dst = kv_smem + slot * TILE_BYTES;
+        mbar_expect_tx(&kv_full[slot], TILE_BYTES);
+        const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
+        const int row0 = (i >> 1) * BKV;
+        tma_load_4d(dst, tm, &kv_full[slot], 0, row0, head, batch);
+        tma_load_4d(dst + HALF_BYTES, tm, &kv_full[slot], 64, row0, head, batch);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);  // A = Q (K-major), B = K (K-major)
+      constexpr uint32_t idesc_pv = make_idesc_bf16(BQ, D, 0, 1);    // A = P (TMEM), B = V (MN-major)
+      const uint32_t q_addr = smem_u32(q_smem);
+      const uint32_t kv_addr = smem_u32(kv_smem);
+      bool ok = true;
+
+      auto issue_qk = [&](int t, int slot) {
+        const uint32_t qa = q_addr + t * TILE_BYTES;
+        const uint32_t ka = kv_addr + slot * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_ss(tmem_base + t * 128, make_smem_desc(qa + off, 16, 1024),
+                  make_smem_desc(ka + off, 16, 1024), idesc_qk, ks != 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int t, int slot, bool accumulate) {
+        const uint32_t va = kv_addr + slot * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BKV / 16; ++ks) {
+          // 16 keys per step: 16 rows of 128 bytes in each half-block; 8 TMEM columns of P.
+          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8,
+                  make_smem_desc(va + ks * 16 * 128, p.v_lbo, p.v_sbo), idesc_pv,
+                  (accumulate || ks != 0) ? 1u : 0u);
+        }
+      };
+
+      ok = mbar_wait(q_full, 0, abort_flag, p.status, 21);
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, 22);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_qk(0, 0);
+        umma_commit(&s_full[0]);
+        issue_qk(1, 0);
+        umma_commit(&s_full[1]);
+        umma_commit(&kv_empty[0]);
+      }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int iv = 2 * j + 1;
+        const int v_slot = iv % KV_SLOTS;
+        if (!mbar_wait(&kv_full[v_slot], (iv / KV_SLOTS) & 1, abort_flag, p.status, 23)) { ok = false; break; }
+        const int ik = 2 * j + 2;
+        const int k_slot = ik % KV_SLOTS;
+        for (int t = 0; t < 2; ++t) {
+          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status, 24)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_pv(t, v_slot, j > 0);
+          if (t == 1) umma_commit(&kv_empty[v_slot]);
+          if (j + 1 < n_kv) {
+            if (t == 0) {
+              if (!mbar_wait(&kv_full[k_slot], (ik / KV_SLOTS) & 1, abort_flag, p.status, 25)) { ok = false; break; }
+              tc_fence_after_sync();
+            }
+            issue_qk(t, k_slot);
+            umma_commit(&s_full[t]);
+            if (t == 1) umma_commit(&kv_empty[k_slot]);
+          } else {
+            umma_commit(&s_full[t]);  // final O_t complete
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int t = warp >> 2;   // query tile / group
+    const int quad = warp & 3;  // TMEM lane quadrant
+    const int row = q0 + t * BQ + quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t s_addr = lane_base + t * 128;
+    const uint32_t o_addr = lane_base + 256 + t * 128;
+    float m_used = 0.f;  // running maximum (already multiplied by scale_log2) used in the exponent
+    float l = 0.f;       // running sum of exp2
+    bool ok = true;
+
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(&s_full[t], j & 1, abort_flag, p.status, 31)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+      tmem_wait_ld();
+
+      const int valid = p.Lk - j * BKV;  // keys of this tile that exist
+      if (valid < BKV) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i >= valid) s[i] = 0xff800000u;  // -inf
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+      const float mx_scaled = mx * p.scale_log2;
+
+      if (j == 0) {
+        m_used = mx_scaled;
+      } else if (__any_sync(0xffffffffu, mx_scaled > m_used + kRescaleThreshold)) {
+        // Move the exponent base for this warp's 32 rows and rescale their O rows in TMEM.  The
+        // barrier just passed also covers the previous P·V of this tile, so O is quiescent.
+        const float m_new = fmaxf(m_used, mx_scaled);
+        const float alpha = ex2(m_used - m_new);
+        l *= alpha;
+        m_used = m_new;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(o_addr + c * 32, o);
+        }
+      }
+
+      const float neg_m = -m_used;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float e0 = ex2(fmaf(__uint_as_float(s[c * 32 + 2 * i]), p.scale_log2, neg_m));
+          const float e1 = ex2(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
+          sum0 += e0;
+          sum1 += e1;
+          pk[i] = pack_bf16(e0, e1);
+        }
+        tmem_st_x16(s_addr + c * 16, pk);
+      }
+      l += sum0 + sum1;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[t]);
+    }
+
+    if (ok && mbar_wait(&s_full[t], n_kv & 1, abort_flag, p.status, 32)) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l;
+      __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + (int64_t)row * p.o_sl;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_x32(o_addr + c * 32, o);
+        tmem_wait_ld();
+        if (row < p.Lq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace attn
+}  // namespace fluxb
+
+using namespace fluxb;
+
+static int encode_qkv_map(CUtensorMap* tm, const void* base, int64_t B, int64_t H, int64_t L,
+                          int64_t sb, int64_t sh, int64_t sl) {
+  // A size-1 dimension may come with any stride; give the encoder a harmless valid one.
+  if (H == 1 || sh == 0) sh = sl * L;
+  if (B == 1 || sb == 0) sb = sh * H;
+  const uint64_t dims[4] = {128, (uint64_t)L, (uint64_t)H, (uint64_t)B};
+  const uint64_t strides[3] = {(uint64_t)sl * 2, (uint64_t)sh * 2, (uint64_t)sb * 2};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return encode_tmap_bf16(tm, base, 4, dims, strides, box);
+}
+
+static uint32_t env_u32(const char* name, uint32_t dflt) {
+  const char* s = getenv(name);
+  if (s == nullptr || *s == 0) return dflt;
+  return (uint32_t)strtoul(s, nullptr, 0);
+}
+
+extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void* o, int64_t B,
+                               int64_t H, int64_t Lq, int64_t Lk, int64_t D, int64_t q_sb,
+                               int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                               int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
+                               int64_t o_sl, float sm_scale, fluxb_stream_t stream) {
+  using namespace fluxb::attn;
+  if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "attention: head_dim %lld (only 128)", (long long)D);
+  if (B < 0 || H < 0 || Lq < 0 || Lk < 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: negative size");
+  if (B == 0 || H == 0 || Lq == 0) return FLUXB_OK;
+  if (Lk == 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: no keys");
+  if (!q || !k || !v || !o) return set_error(FLUXB_ERR_BAD_ARG, "attention: null pointer");
+  if (H > 65535 || B > 65535 || Lq > (1 << 30) || Lk > (1 << 30))
+    return set_error(FLUXB_ERR_UNSUPPORTED, "attention: dimension too large");
+  const int64_t strides[] = {q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, v_sb, v_sh, v_sl, o_sb, o_sh, o_sl};
+  for (int64_t s : strides)
+    if (s % 8 || s < 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: strides must be non-negative multiples of 8 elements");
+  if (q_sl < 128 || k_sl < 128 || v_sl < 128 || o_sl < 128)
+    return set_error(FLUXB_ERR_BAD_ARG, "attention: row stride below head_dim");
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return set_error(FLUXB_ERR_BAD_ARG, "attention: pointers must be 16-byte aligned");
+
+  CUtensorMap tm_q, tm_k, tm_v;
+  int rc = encode_qkv_map(&tm_q, q, B, H, Lq, q_sb, q_sh, q_sl);
+  if (rc == FLUXB_OK) rc = encode_qkv_map(&tm_k, k, B, H, Lk, k_sb, k_sh, k_sl);
+  if (rc == FLUXB_OK) rc = encode_qkv_map(&tm_v, v, B, H, Lk, v_sb, v_sh, v_sl);
+  if (rc != FLUXB_OK) return rc;
+
+  Params p;
+  p.o = static_cast<__nv_bfloat16*>(o);
+  p.o_sb = o_sb; p.o_sh = o_sh; p.o_sl = o_sl;
+  p.Lq = (int)Lq; p.Lk = (int)Lk;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  // V is consumed as the MN-major operand: 8-key groups are 1024 bytes apart (stride offset)
+  // and the two 64-wide halves of head_dim are 16384 bytes apart (leading offset).
+  p.v_lbo = env_u32("FLUXB_ATTN_V_LBO", HALF_BYTES);
+  p.v_sbo = env_u32("FLUXB_ATTN_V_SBO", 1024);
+  p.status = device_status_ptr();
+
+  cudaError_t e = cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: cannot set shared memory size: %s", cudaGetErrorString(e));
+  dim3 grid((unsigned)((Lq + 2 * BQ - 1) / (2 * BQ)), (unsigned)H, (unsigned)B);
+  attn_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: launch failed: %s", cudaGetErrorString(e));
+  return FLUXB_OK;
+}

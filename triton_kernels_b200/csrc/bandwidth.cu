@@ -1,0 +1,933 @@
+// HBM-bound kernels of the Flux DiT block path: LayerNorm + adaLN modulation, RMSNorm
+// (forward and backward), RoPE, fused q/k/v assembly (split + QK-RMSNorm + RoPE + head-major
+// concat), modulation scale/shift and gate/residual, SiLU, and the small-batch modulation
+// projection (a GEMV over bf16 weights).
+//
+// Common shape of every kernel: 16-byte vector loads/stores, one row (or row segment) held in
+// registers, fp32 statistics with a centred second pass, reductions by warp shuffles only.
+// Algorithmic traffic is "every input once, every output once"; nothing is staged through
+// global scratch.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace fluxb {
+
+// ----------------------------------------------------------------------------------------
+// 16-byte vector access for fp32 / bf16 rows, presented to the math as fp32 lanes.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  float v[4];
+  __device__ __forceinline__ void unpack(const uint4& t) {
+    v[0] = __uint_as_float(t.x); v[1] = __uint_as_float(t.y);
+    v[2] = __uint_as_float(t.z); v[3] = __uint_as_float(t.w);
+  }
+  __device__ __forceinline__ void load(const float* p) {
+    float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  __device__ __forceinline__ void load_nc(const float* p) {
+    float4 t = __ldg(reinterpret_cast<const float4*>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  __device__ __forceinline__ void store(float* p) const {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  float v[8];
+  __device__ __forceinline__ void unpack(const uint4& t) {
+    v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
+    v[4] = bf16_lo(t.z); v[5] = bf16_hi(t.z); v[6] = bf16_lo(t.w); v[7] = bf16_hi(t.w);
+  }
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+    unpack(*reinterpret_cast<const uint4*>(p));
+  }
+  __device__ __forceinline__ void load_nc(const __nv_bfloat16* p) {
+    unpack(__ldg(reinterpret_cast<const uint4*>(p)));
+  }
+  __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+    uint4 t;
+    t.x = pack_bf16(v[0], v[1]); t.y = pack_bf16(v[2], v[3]);
+    t.z = pack_bf16(v[4], v[5]); t.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = t;
+  }
+};
+
+// Makes the compiler forget what it knows about a packed vector, so the fp32 widening is redone
+// at each use instead of being kept live (which doubles the registers of a bf16 row).
+__device__ __forceinline__ void forget(uint4& t) {
+  asm volatile("" : "+r"(t.x), "+r"(t.y), "+r"(t.z), "+r"(t.w));
+}
+
+template <int G>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ----------------------------------------------------------------------------------------
+// LayerNorm (no affine) + modulation.  G lanes own one row; each lane holds VPL vectors.
+// cols == G * VPL * Vec<T>::N.
+// ----------------------------------------------------------------------------------------
+template <typename T, int G, int VPL>
+__global__ void __launch_bounds__(256, (VPL <= 12 ? 3 : (VPL <= 24 ? 2 : 1)))
+ln_mod_rows_kernel(const T* __restrict__ x, const T* __restrict__ scale, const T* __restrict__ shift,
+                   T* __restrict__ y, int64_t rows, int cols, int64_t rows_per_batch, int64_t x_ld,
+                   int64_t y_ld, int64_t mod_stride, float eps) {
+  constexpr int VN = Vec<T>::N;
+  const int lane_in_group = threadIdx.x % G;
+  const int64_t groups_per_block = blockDim.x / G;
+  const int64_t row = blockIdx.x * groups_per_block + threadIdx.x / G;
+  const bool active = row < rows;
+  const int64_t r = active ? row : rows - 1;  // keep every lane in the shuffles
+
+  // The row stays packed (16 bytes per register quad) so that a 3072-wide bf16 row costs 48
+  // registers per lane, not 96; values are widened to fp32 where they are used.
+  uint4 raw[VPL];
+  const T* xr = x + r * x_ld;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+    raw[i] = *reinterpret_cast<const uint4*>(xr + (i * G + lane_in_group) * VN);
+
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    Vec<T> t;
+    t.unpack(raw[i]);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) s += t.v[j];
+  }
+  const float mean = group_sum<G>(s) / cols;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    Vec<T> t;
+    forget(raw[i]);
+    t.unpack(raw[i]);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) {
+      float d = t.v[j] - mean;
+      q += d * d;
+    }
+  }
+  const float rstd = rsqrtf(group_sum<G>(q) / cols + eps);
+
+  const int64_t b = r / rows_per_batch;
+  const T* sc = scale + b * mod_stride;
+  const T* sh = shift + b * mod_stride;
+  T* yr = y + r * y_ld;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * G + lane_in_group) * VN;
+    Vec<T> t, a, d;
+    forget(raw[i]);
+    t.unpack(raw[i]);
+    a.load_nc(sc + c);
+    d.load_nc(sh + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) t.v[j] = (t.v[j] - mean) * rstd * (1.0f + a.v[j]) + d.v[j];
+    if (active) t.store(yr + c);
+  }
+}
+
+// Any cols (multiple of the vector width): one warp per row, three passes over the row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ln_mod_generic_kernel(const T* __restrict__ x, const T* __restrict__ scale,
+                      const T* __restrict__ shift, T* __restrict__ y, int64_t rows, int cols,
+                      int64_t rows_per_batch, int64_t x_ld, int64_t y_ld, int64_t mod_stride,
+                      float eps) {
+  constexpr int VN = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (row >= rows) return;
+  const T* xr = x + row * x_ld;
+  float s = 0.f;
+  for (int c = lane * VN; c < cols; c += 32 * VN) {
+    Vec<T> t;
+    t.load(xr + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) s += t.v[j];
+  }
+  const float mean = warp_sum(s) / cols;
+  float q = 0.f;
+  for (int c = lane * VN; c < cols; c += 32 * VN) {
+    Vec<T> t;
+    t.load(xr + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) {
+      float d = t.v[j] - mean;
+      q += d * d;
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / cols + eps);
+  const int64_t b = row / rows_per_batch;
+  const T* sc = scale + b * mod_stride;
+  const T* sh = shift + b * mod_stride;
+  T* yr = y + row * y_ld;
+  for (int c = lane * VN; c < cols; c += 32 * VN) {
+    Vec<T> t, a, d;
+    t.load(xr + c);
+    a.load_nc(sc + c);
+    d.load_nc(sh + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) t.v[j] = (t.v[j] - mean) * rstd * (1.0f + a.v[j]) + d.v[j];
+    t.store(yr + c);
+  }
+}
+
+template <typename T>
+static int launch_ln_mod(const void* x, const void* scale, const void* shift, void* y, int64_t rows,
+                         int64_t cols, int64_t rpb, int64_t x_ld, int64_t y_ld, int64_t mod_stride,
+                         float eps, cudaStream_t st) {
+  constexpr int VN = Vec<T>::N;
+  const T* xp = static_cast<const T*>(x);
+  const T* sc = static_cast<const T*>(scale);
+  const T* sh = static_cast<const T*>(shift);
+  T* yp = static_cast<T*>(y);
+  const int64_t vecs = cols / VN;
+#define FLUXB_LN_CASE(G, VPL)                                                                  \
+  if (vecs == (G) * (VPL)) {                                                                   \
+    const int64_t gpb = 256 / (G);                                                             \
+    ln_mod_rows_kernel<T, G, VPL><<<(unsigned)((rows + gpb - 1) / gpb), 256, 0, st>>>(         \
+        xp, sc, sh, yp, rows, (int)cols, rpb, x_ld, y_ld, mod_stride, eps);                    \
+    return FLUXB_OK;                                                                           \
+  }
+  FLUXB_LN_CASE(32, 1) FLUXB_LN_CASE(32, 2) FLUXB_LN_CASE(32, 3) FLUXB_LN_CASE(32, 4)
+  FLUXB_LN_CASE(32, 6) FLUXB_LN_CASE(32, 8) FLUXB_LN_CASE(32, 12) FLUXB_LN_CASE(32, 16)
+  FLUXB_LN_CASE(32, 24)
+#undef FLUXB_LN_CASE
+  ln_mod_generic_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+      xp, sc, sh, yp, rows, (int)cols, rpb, x_ld, y_ld, mod_stride, eps);
+  return FLUXB_OK;
+}
+
+// ----------------------------------------------------------------------------------------
+// RMSNorm forward.  Input rows addressed through a 3-level stride (head-split views).
+// ----------------------------------------------------------------------------------------
+struct RowAddr {
+  int64_t n1, n2, s0, s1, s2;
+  __device__ __forceinline__ int64_t offset(int64_t row) const {
+    const int64_t i2 = row % n2;
+    const int64_t t = row / n2;
+    return (t / n1) * s0 + (t % n1) * s1 + i2 * s2;
+  }
+};
+
+template <typename T, int G, int VPL>
+__global__ void __launch_bounds__(256, (VPL <= 12 ? 3 : (VPL <= 24 ? 2 : 1)))
+rms_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                float* __restrict__ rstd_out, int64_t rows, int cols, RowAddr addr, float eps) {
+  constexpr int VN = Vec<T>::N;
+  const int lig = threadIdx.x % G;
+  const int64_t gpb = blockDim.x / G;
+  const int64_t row = blockIdx.x * gpb + threadIdx.x / G;
+  const bool active = row < rows;
+  const int64_t r = active ? row : rows - 1;
+  const T* xr = x + addr.offset(r);
+  uint4 raw[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) raw[i] = *reinterpret_cast<const uint4*>(xr + (i * G + lig) * VN);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    Vec<T> t;
+    t.unpack(raw[i]);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) s += t.v[j] * t.v[j];
+  }
+  const float rstd = rsqrtf(group_sum<G>(s) / cols + eps);
+  if (active && rstd_out != nullptr && lig == 0) rstd_out[r] = rstd;
+  T* yr = y + r * (int64_t)cols;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = (i * G + lig) * VN;
+    Vec<T> t, wv;
+    forget(raw[i]);
+    t.unpack(raw[i]);
+    wv.load_nc(w + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) t.v[j] = t.v[j] * rstd * wv.v[j];
+    if (active) t.store(yr + c);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                   float* __restrict__ rstd_out, int64_t rows, int cols, RowAddr addr, float eps) {
+  constexpr int VN = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (row >= rows) return;
+  const T* xr = x + addr.offset(row);
+  float s = 0.f;
+  for (int c = lane * VN; c < cols; c += 32 * VN) {
+    Vec<T> t;
+    t.load(xr + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) s += t.v[j] * t.v[j];
+  }
+  const float rstd = rsqrtf(warp_sum(s) / cols + eps);
+  if (rstd_out != nullptr && lane == 0) rstd_out[row] = rstd;
+  T* yr = y + row * (int64_t)cols;
+  for (int c = lane * VN; c < cols; c += 32 * VN) {
+    Vec<T> t, wv;
+    t.load(xr + c);
+    wv.load_nc(w + c);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) t.v[j] = t.v[j] * rstd * wv.v[j];
+    t.store(yr + c);
+  }
+}
+
+template <typename T>
+static int launch_rms(const void* x, const void* w, void* y, float* rstd, int64_t rows, int64_t cols,
+                      RowAddr addr, float eps, cudaStream_t st) {
+  constexpr int VN = Vec<T>::N;
+  const T* xp = static_cast<const T*>(x);
+  const T* wp = static_cast<const T*>(w);
+  T* yp = static_cast<T*>(y);
+  const int64_t vecs = cols / VN;
+#define FLUXB_RMS_CASE(G, VPL)                                                                 \
+  if (vecs == (G) * (VPL)) {                                                                   \
+    const int64_t gpb = 256 / (G);                                                             \
+    rms_rows_kernel<T, G, VPL><<<(unsigned)((rows + gpb - 1) / gpb), 256, 0, st>>>(            \
+        xp, wp, yp, rstd, rows, (int)cols, addr, eps);                                         \
+    return FLUXB_OK;                                                                           \
+  }
+  FLUXB_RMS_CASE(8, 1) FLUXB_RMS_CASE(16, 1) FLUXB_RMS_CASE(32, 1) FLUXB_RMS_CASE(32, 2)
+  FLUXB_RMS_CASE(32, 3) FLUXB_RMS_CASE(32, 4) FLUXB_RMS_CASE(32, 6) FLUXB_RMS_CASE(32, 8)
+  FLUXB_RMS_CASE(32, 12) FLUXB_RMS_CASE(32, 16) FLUXB_RMS_CASE(32, 24)
+#undef FLUXB_RMS_CASE
+  rms_generic_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(xp, wp, yp, rstd, rows,
+                                                                    (int)cols, addr, eps);
+  return FLUXB_OK;
+}
+
+// ----------------------------------------------------------------------------------------
+// RMSNorm backward.  One warp per row for dx; each block also accumulates its rows' dw
+// contributions in registers and writes one fp32 partial row per block (no atomics, so the
+// result is deterministic); the caller sums the partial rows.
+// ----------------------------------------------------------------------------------------
+constexpr int kRmsBwdRowsPerBlock = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+               const float* __restrict__ rstd, T* __restrict__ dx, float* __restrict__ dw_partial,
+               int64_t rows, int cols) {
+  constexpr int VN = Vec<T>::N;
+  extern __shared__ float dw_smem[];  // [8 warps][cols]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float* my_dw = dw_smem + (int64_t)warp * cols;
+  for (int c = lane; c < cols; c += 32) my_dw[c] = 0.f;
+  __syncwarp();
+  const int64_t row0 = (int64_t)blockIdx.x * kRmsBwdRowsPerBlock;
+  for (int rr = warp; rr < kRmsBwdRowsPerBlock; rr += 8) {
+    const int64_t row = row0 + rr;
+    if (row >= rows) break;
+    const T* dyr = dy + row * (int64_t)cols;
+    const T* xr = x + row * (int64_t)cols;
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int c = lane * VN; c < cols; c += 32 * VN) {
+      Vec<T> a, b, ww;
+      a.load(dyr + c);
+      b.load(xr + c);
+      ww.load_nc(w + c);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) dot += a.v[j] * ww.v[j] * b.v[j];
+    }
+    dot = warp_sum(dot);
+    const float coef = -rs * rs * rs * dot / cols;
+    T* dxr = dx + row * (int64_t)cols;
+    for (int c = lane * VN; c < cols; c += 32 * VN) {
+      Vec<T> a, b, ww, o;
+      a.load(dyr + c);
+      b.load(xr + c);
+      ww.load_nc(w + c);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) {
+        o.v[j] = rs * a.v[j] * ww.v[j] + coef * b.v[j];
+        my_dw[c + j] += a.v[j] * b.v[j] * rs;
+      }
+      o.store(dxr + c);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) s += dw_smem[(int64_t)wi * cols + c];
+    dw_partial[(int64_t)blockIdx.x * cols + c] = s;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// RoPE with a general 2x2 table.  A thread owns 4 pairs (8 bf16 / 2x4 fp32) of one token and
+// walks HG heads with the table entries held in registers.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  Vec<__nv_bfloat16> t;
+  t.load(p);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = t.v[j];
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 t;
+  t.x = pack_bf16(v[0], v[1]); t.y = pack_bf16(v[2], v[3]);
+  t.z = pack_bf16(v[4], v[5]); t.w = pack_bf16(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = t;
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// f[i] = {f00, f01, f10, f11} for pair i;  out[2i] = f00 x0 + f01 x1, out[2i+1] = f10 x0 + f11 x1
+__device__ __forceinline__ void rotate8(const float4 (&f)[4], const float (&x)[8], float (&o)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = f[i].x * x[2 * i] + f[i].y * x[2 * i + 1];
+    o[2 * i + 1] = f[i].z * x[2 * i] + f[i].w * x[2 * i + 1];
+  }
+}
+
+template <typename T, int HG>
+__global__ void __launch_bounds__(256)
+rope_kernel(const T* __restrict__ q, const T* __restrict__ k, const float* __restrict__ pe,
+            T* __restrict__ oq, T* __restrict__ ok, int64_t BH, int64_t L, int D) {
+  const int chunks = D / 8;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= L * chunks) return;
+  const int64_t l = idx / chunks;
+  const int c = (int)(idx % chunks);
+  float4 f[4];
+  const float4* pr = reinterpret_cast<const float4*>(pe) + l * (D / 2) + c * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) f[i] = __ldg(pr + i);
+  const int64_t bh0 = (int64_t)blockIdx.y * HG;
+  const int64_t off0 = l * D + c * 8;
+  float xq[HG][8], xk[HG][8];
+#pragma unroll
+  for (int h = 0; h < HG; ++h) {
+    if (bh0 + h < BH) {
+      load8<T>(q + (bh0 + h) * L * D + off0, xq[h]);
+      load8<T>(k + (bh0 + h) * L * D + off0, xk[h]);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < HG; ++h) {
+    if (bh0 + h < BH) {
+      float o[8];
+      rotate8(f, xq[h], o);
+      store8<T>(oq + (bh0 + h) * L * D + off0, o);
+      rotate8(f, xk[h], o);
+      store8<T>(ok + (bh0 + h) * L * D + off0, o);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Fused q/k/v assembly: split + per-head RMSNorm of q,k + RoPE + head-major concat of up to
+// two token streams.  16 lanes own one (token, head) row of 128; a thread walks HG heads of
+// its token with the rope entries in registers.  bf16 only, D = 128.
+// ----------------------------------------------------------------------------------------
+struct QkvPrepArgs {
+  const __nv_bfloat16* src[2];
+  int64_t len[2];
+  int64_t ld[2];
+  const __nv_bfloat16* qscale[2];
+  const __nv_bfloat16* kscale[2];
+  const float* pe;
+  __nv_bfloat16* q;
+  __nv_bfloat16* k;
+  __nv_bfloat16* v;
+  int64_t B, H, L;
+  float eps;
+};
+
+template <int HG>
+__global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
+  constexpr int D = 128;
+  const int lane16 = threadIdx.x & 15;
+  const int64_t tok = (int64_t)blockIdx.x * (blockDim.x / 16) + threadIdx.x / 16;  // b * L + l
+  const bool active = tok < a.B * a.L;
+  const int64_t t = active ? tok : a.B * a.L - 1;
+  const int64_t b = t / a.L;
+  const int64_t l = t % a.L;
+  const int s = (l < a.len[0]) ? 0 : 1;
+  const int64_t ls = (s == 0) ? l : l - a.len[0];
+  const __nv_bfloat16* row = a.src[s] + (b * a.len[s] + ls) * a.ld[s];
+  const int64_t HD = a.H * D;
+
+  float4 f[4];
+  const bool do_rope = a.pe != nullptr;
+  if (do_rope) {
+    const float4* pr = reinterpret_cast<const float4*>(a.pe) + l * (D / 2) + lane16 * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = __ldg(pr + i);
+  }
+  const bool do_norm = a.qscale[s] != nullptr;
+  float wq[8], wk[8];
+  if (do_norm) {
+    load8<__nv_bfloat16>(a.qscale[s] + lane16 * 8, wq);
+    load8<__nv_bfloat16>(a.kscale[s] + lane16 * 8, wk);
+  }
+
+  const int64_t h0 = (int64_t)blockIdx.y * HG;
+  uint4 raw[HG][3];
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) {
+    const int64_t h = h0 + hh;
+    if (h < a.H) {
+#pragma unroll
+      for (int part = 0; part < 3; ++part)
+        raw[hh][part] = *reinterpret_cast<const uint4*>(row + part * HD + h * D + lane16 * 8);
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < HG; ++hh) {
+    const int64_t h = h0 + hh;
+    if (h >= a.H) continue;  // uniform across the block (depends on blockIdx.y only)
+    const int64_t out_off = ((b * a.H + h) * a.L + l) * D + lane16 * 8;
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+      Vec<__nv_bfloat16> xv;
+      xv.unpack(raw[hh][part]);
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = xv.v[j];
+      if (do_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+        const float rstd = rsqrtf(group_sum<16>(ss) / D + a.eps);
+        const float* wsel = part == 0 ? wq : wk;
+        // Normalised values stay in fp32 through the rotation: one rounding, at the store.
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = x[j] * rstd * wsel[j];
+      }
+      float o[8];
+      if (do_rope) {
+        rotate8(f, x, o);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = x[j];
+      }
+      if (active) store8<__nv_bfloat16>((part == 0 ? a.q : a.k) + out_off, o);
+    }
+    if (active) *reinterpret_cast<uint4*>(a.v + out_off) = raw[hh][2];
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Elementwise modulation kernels and SiLU.
+// ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+mod_scale_shift_kernel(const T* __restrict__ x, const T* __restrict__ mod, T* __restrict__ out,
+                       int64_t nvec, int64_t L, int C, int64_t mod_row_stride, int shift_chunk,
+                       int scale_chunk) {
+  constexpr int VN = Vec<T>::N;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const int64_t e = i * VN;
+  const int c = (int)(e % C);
+  const int64_t b = e / ((int64_t)C * L);
+  Vec<T> xv, sc, sh;
+  xv.load(x + e);
+  sh.load_nc(mod + b * mod_row_stride + (int64_t)shift_chunk * C + c);
+  sc.load_nc(mod + b * mod_row_stride + (int64_t)scale_chunk * C + c);
+#pragma unroll
+  for (int j = 0; j < VN; ++j) xv.v[j] = (sc.v[j] + 1.0f) * xv.v[j] + sh.v[j];
+  xv.store(out + e);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+mod_gate_proj_kernel(const T* __restrict__ resid, const T* __restrict__ mod,
+                     const T* __restrict__ proj, T* __restrict__ out, int64_t nvec, int64_t L, int C,
+                     int64_t mod_row_stride, int gate_chunk) {
+  constexpr int VN = Vec<T>::N;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const int64_t e = i * VN;
+  const int c = (int)(e % C);
+  const int64_t b = e / ((int64_t)C * L);
+  Vec<T> r, p, g;
+  r.load(resid + e);
+  p.load(proj + e);
+  g.load_nc(mod + b * mod_row_stride + (int64_t)gate_chunk * C + c);
+#pragma unroll
+  for (int j = 0; j < VN; ++j) r.v[j] = r.v[j] + g.v[j] * p.v[j];
+  r.store(out + e);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n) {
+  constexpr int VN = Vec<T>::N;
+  const int64_t e = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VN;
+  if (e + VN <= n) {
+    Vec<T> v;
+    v.load(x + e);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) v.v[j] = silu_f(v.v[j]);
+    v.store(out + e);
+  } else {
+    for (int64_t i = e; i < n; ++i) out[i] = static_cast<T>(silu_f(static_cast<float>(x[i])));
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Modulation projection: out[b,n] = sum_k act(vec[b,k]) w[n,k] + bias[n], bf16 weights read
+// exactly once per batch tile of BT rows.  One warp per output column n; act(vec) staged in
+// shared memory as fp32.
+// ----------------------------------------------------------------------------------------
+template <int BT>
+__global__ void __launch_bounds__(256)
+mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __restrict__ w,
+                const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
+                int K, int64_t b0, int apply_silu) {
+  extern __shared__ float sv[];  // [BT][K]
+  for (int i = threadIdx.x; i < BT * K; i += blockDim.x) {
+    const int bb = i / K, kk = i % K;
+    float t = __bfloat162float(vec[(b0 + bb) * K + kk]);
+    if (apply_silu) t = silu_f(t);  // kept in fp32: no intermediate rounding
+    sv[i] = t;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int64_t n = (int64_t)blockIdx.x * 8 + warp; n < N; n += (int64_t)gridDim.x * 8) {
+    const __nv_bfloat16* wr = w + n * K;
+    float acc[BT];
+#pragma unroll
+    for (int bb = 0; bb < BT; ++bb) acc[bb] = 0.f;
+    for (int k0 = lane * 8; k0 < K; k0 += 256) {
+      Vec<__nv_bfloat16> wv;
+      wv.load_nc(wr + k0);
+#pragma unroll
+      for (int bb = 0; bb < BT; ++bb) {
+        const float4 a0 = *reinterpret_cast<const float4*>(sv + bb * K + k0);
+        const float4 a1 = *reinterpret_cast<const float4*>(sv + bb * K + k0 + 4);
+        acc[bb] += wv.v[0] * a0.x + wv.v[1] * a0.y + wv.v[2] * a0.z + wv.v[3] * a0.w +
+                   wv.v[4] * a1.x + wv.v[5] * a1.y + wv.v[6] * a1.z + wv.v[7] * a1.w;
+      }
+    }
+#pragma unroll
+    for (int bb = 0; bb < BT; ++bb) {
+      const float s = warp_sum(acc[bb]);
+      if (lane == 0) {
+        const float bv = bias != nullptr ? __bfloat162float(bias[n]) : 0.f;
+        out[(b0 + bb) * N + n] = __float2bfloat16_rn(s + bv);
+      }
+    }
+  }
+}
+
+}  // namespace fluxb
+
+// ========================================================================================
+// C ABI
+// ========================================================================================
+using namespace fluxb;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  return FLUXB_OK;
+}
+static inline int vec_elems(int dtype) { return dtype == FLUXB_BF16 ? 8 : 4; }
+
+extern "C" int fluxb_layer_norm_modulation(const void* x, const void* scale, const void* shift,
+                                           void* y, int64_t rows, int64_t cols,
+                                           int64_t rows_per_batch, int64_t x_ld, int64_t y_ld,
+                                           int64_t mod_stride, float eps, int dtype,
+                                           fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "layer_norm_modulation: dtype %d", dtype);
+  if (rows < 0 || cols <= 0 || rows_per_batch <= 0)
+    return set_error(FLUXB_ERR_BAD_ARG, "layer_norm_modulation: bad sizes");
+  if (rows == 0) return FLUXB_OK;
+  if (!x || !scale || !shift || !y)
+    return set_error(FLUXB_ERR_BAD_ARG, "layer_norm_modulation: null pointer");
+  const int vn = vec_elems(dtype);
+  if (cols % vn || x_ld % vn || y_ld % vn || mod_stride % vn || !aligned16(x) || !aligned16(y) ||
+      !aligned16(scale) || !aligned16(shift))
+    return set_error(FLUXB_ERR_BAD_ARG,
+                     "layer_norm_modulation: cols/strides must be multiples of %d elements and "
+                     "pointers 16-byte aligned", vn);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FLUXB_BF16)
+    launch_ln_mod<__nv_bfloat16>(x, scale, shift, y, rows, cols, rows_per_batch, x_ld, y_ld,
+                                 mod_stride, eps, st);
+  else
+    launch_ln_mod<float>(x, scale, shift, y, rows, cols, rows_per_batch, x_ld, y_ld, mod_stride, eps,
+                         st);
+  return launch_status("layer_norm_modulation");
+}
+
+extern "C" int fluxb_rms_norm(const void* x, const void* w, void* y, float* rstd, int64_t n0,
+                              int64_t n1, int64_t n2, int64_t cols, int64_t s0, int64_t s1,
+                              int64_t s2, float eps, int dtype, fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "rms_norm: dtype %d", dtype);
+  if (n0 < 0 || n1 < 0 || n2 < 0 || cols <= 0) return set_error(FLUXB_ERR_BAD_ARG, "rms_norm: bad sizes");
+  const int64_t rows = n0 * n1 * n2;
+  if (rows == 0) return FLUXB_OK;
+  if (!x || !w || !y) return set_error(FLUXB_ERR_BAD_ARG, "rms_norm: null pointer");
+  const int vn = vec_elems(dtype);
+  if (cols % vn || s0 % vn || s1 % vn || s2 % vn || !aligned16(x) || !aligned16(y) || !aligned16(w))
+    return set_error(FLUXB_ERR_BAD_ARG,
+                     "rms_norm: cols/strides must be multiples of %d elements and pointers 16-byte "
+                     "aligned", vn);
+  RowAddr addr{n1, n2, s0, s1, s2};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FLUXB_BF16)
+    launch_rms<__nv_bfloat16>(x, w, y, rstd, rows, cols, addr, eps, st);
+  else
+    launch_rms<float>(x, w, y, rstd, rows, cols, addr, eps, st);
+  return launch_status("rms_norm");
+}
+
+extern "C" int fluxb_rms_norm_bwd_partial_rows(int64_t rows) {
+  return (int)((rows + kRmsBwdRowsPerBlock - 1) / kRmsBwdRowsPerBlock);
+}
+
+extern "C" int fluxb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                                  void* dx, float* dw_partial, int64_t rows, int64_t cols, int dtype,
+                                  fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "rms_norm_bwd: dtype %d", dtype);
+  if (rows < 0 || cols <= 0) return set_error(FLUXB_ERR_BAD_ARG, "rms_norm_bwd: bad sizes");
+  if (rows == 0) return FLUXB_OK;
+  if (!dy || !x || !w || !rstd || !dx || !dw_partial)
+    return set_error(FLUXB_ERR_BAD_ARG, "rms_norm_bwd: null pointer");
+  const int vn = vec_elems(dtype);
+  if (cols % vn || !aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx))
+    return set_error(FLUXB_ERR_BAD_ARG, "rms_norm_bwd: cols must be a multiple of %d, pointers 16-byte aligned", vn);
+  const size_t smem = (size_t)8 * cols * sizeof(float);
+  if (smem > 200 * 1024) return set_error(FLUXB_ERR_UNSUPPORTED, "rms_norm_bwd: cols %lld too large", (long long)cols);
+  const unsigned grid = (unsigned)fluxb_rms_norm_bwd_partial_rows(rows);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FLUXB_BF16) {
+    auto kern = rms_bwd_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+                                  static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx),
+                                  dw_partial, rows, (int)cols);
+  } else {
+    auto kern = rms_bwd_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<grid, 256, smem, st>>>(static_cast<const float*>(dy), static_cast<const float*>(x),
+                                  static_cast<const float*>(w), rstd, static_cast<float*>(dx), dw_partial,
+                                  rows, (int)cols);
+  }
+  return launch_status("rms_norm_bwd");
+}
+
+extern "C" int fluxb_rope(const void* q, const void* k, const float* pe, void* oq, void* ok,
+                          int64_t BH, int64_t L, int64_t D, int dtype, fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "rope: dtype %d", dtype);
+  if (BH < 0 || L < 0 || D <= 0 || D % 8) return set_error(FLUXB_ERR_BAD_ARG, "rope: D must be a positive multiple of 8");
+  if (BH == 0 || L == 0) return FLUXB_OK;
+  if (!q || !k || !pe || !oq || !ok) return set_error(FLUXB_ERR_BAD_ARG, "rope: null pointer");
+  if (!aligned16(q) || !aligned16(k) || !aligned16(pe) || !aligned16(oq) || !aligned16(ok))
+    return set_error(FLUXB_ERR_BAD_ARG, "rope: pointers must be 16-byte aligned");
+  constexpr int HG = 4;
+  const int64_t threads = L * (D / 8);
+  dim3 grid((unsigned)((threads + 255) / 256), (unsigned)((BH + HG - 1) / HG));
+  if (grid.y > 65535) return set_error(FLUXB_ERR_UNSUPPORTED, "rope: batch*heads too large");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FLUXB_BF16)
+    rope_kernel<__nv_bfloat16, HG><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), pe,
+        static_cast<__nv_bfloat16*>(oq), static_cast<__nv_bfloat16*>(ok), BH, L, (int)D);
+  else
+    rope_kernel<float, HG><<<grid, 256, 0, st>>>(static_cast<const float*>(q),
+                                                 static_cast<const float*>(k), pe,
+                                                 static_cast<float*>(oq), static_cast<float*>(ok), BH,
+                                                 L, (int)D);
+  return launch_status("rope");
+}
+
+extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
+                              const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
+                              const void* qscale1, const void* kscale1, const float* pe, void* q,
+                              void* k, void* v, int64_t B, int64_t H, int64_t D, float eps,
+                              fluxb_stream_t stream) {
+  if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "qkv_prep: head_dim %lld (only 128)", (long long)D);
+  if (B < 0 || H <= 0 || L0 < 0 || L1 < 0) return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: bad sizes");
+  const int64_t L = L0 + L1;
+  if (B == 0 || L == 0) return FLUXB_OK;
+  if (!q || !k || !v || (L0 > 0 && !src0) || (L1 > 0 && !src1))
+    return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: null pointer");
+  if ((qscale0 == nullptr) != (kscale0 == nullptr) || (L1 > 0 && ((qscale1 == nullptr) != (kscale1 == nullptr))) ||
+      (L0 > 0 && L1 > 0 && ((qscale0 == nullptr) != (qscale1 == nullptr))))
+    return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: norm scales must be given for q and k of every stream or for none");
+  if ((L0 > 0 && (ld0 < 3 * H * D || ld0 % 8)) || (L1 > 0 && (ld1 < 3 * H * D || ld1 % 8)))
+    return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: row stride must be >= 3*H*D and a multiple of 8");
+  if (!aligned16(src0) || !aligned16(src1) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
+      !aligned16(pe) || !aligned16(qscale0) || !aligned16(kscale0) || !aligned16(qscale1) || !aligned16(kscale1))
+    return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: pointers must be 16-byte aligned");
+  QkvPrepArgs a;
+  a.src[0] = static_cast<const __nv_bfloat16*>(src0);
+  a.src[1] = static_cast<const __nv_bfloat16*>(src1);
+  a.len[0] = L0; a.len[1] = L1;
+  a.ld[0] = ld0; a.ld[1] = ld1;
+  a.qscale[0] = static_cast<const __nv_bfloat16*>(qscale0);
+  a.kscale[0] = static_cast<const __nv_bfloat16*>(kscale0);
+  a.qscale[1] = static_cast<const __nv_bfloat16*>(qscale1);
+  a.kscale[1] = static_cast<const __nv_bfloat16*>(kscale1);
+  if (L0 == 0) {  // single stream given as stream 1: make it stream 0
+    a.src[0] = a.src[1]; a.len[0] = L1; a.ld[0] = ld1; a.qscale[0] = a.qscale[1]; a.kscale[0] = a.kscale[1];
+    a.len[1] = 0;
+  }
+  a.pe = pe;
+  a.q = static_cast<__nv_bfloat16*>(q);
+  a.k = static_cast<__nv_bfloat16*>(k);
+  a.v = static_cast<__nv_bfloat16*>(v);
+  a.B = B; a.H = H; a.L = L; a.eps = eps;
+  constexpr int HG = 4;
+  dim3 grid((unsigned)((B * L + 15) / 16), (unsigned)((H + HG - 1) / HG));
+  qkv_prep_kernel<HG><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return launch_status("qkv_prep");
+}
+
+template <typename T>
+static void launch_scale_shift(const void* x, const void* mod, void* out, int64_t B, int64_t L,
+                               int64_t C, int64_t mrs, int is_mod1, cudaStream_t st) {
+  const int64_t nvec = B * L * C / Vec<T>::N;
+  mod_scale_shift_kernel<T><<<(unsigned)((nvec + 255) / 256), 256, 0, st>>>(
+      static_cast<const T*>(x), static_cast<const T*>(mod), static_cast<T*>(out), nvec, L, (int)C, mrs,
+      is_mod1 ? 0 : 3, is_mod1 ? 1 : 4);
+}
+
+extern "C" int fluxb_modulation_scale_shift(const void* x, const void* mod, void* out, int64_t B,
+                                            int64_t L, int64_t C, int64_t mod_row_stride,
+                                            int is_mod1, int dtype, fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "modulation_scale_shift: dtype %d", dtype);
+  if (B < 0 || L < 0 || C <= 0) return set_error(FLUXB_ERR_BAD_ARG, "modulation_scale_shift: bad sizes");
+  if (B * L == 0) return FLUXB_OK;
+  const int vn = vec_elems(dtype);
+  if (!x || !mod || !out || C % vn || mod_row_stride % vn || !aligned16(x) || !aligned16(mod) || !aligned16(out))
+    return set_error(FLUXB_ERR_BAD_ARG, "modulation_scale_shift: null/misaligned pointer or C not a multiple of %d", vn);
+  if (mod_row_stride < (is_mod1 ? 2 : 5) * C)
+    return set_error(FLUXB_ERR_BAD_ARG, "modulation_scale_shift: modulation row too short for the chunks asked");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FLUXB_BF16) launch_scale_shift<__nv_bfloat16>(x, mod, out, B, L, C, mod_row_stride, is_mod1, st);
+  else launch_scale_shift<float>(x, mod, out, B, L, C, mod_row_stride, is_mod1, st);
+  return launch_status("modulation_scale_shift");
+}
+
+template <typename T>
+static void launch_gate_proj(const void* r, const void* mod, const void* p, void* out, int64_t B,
+                             int64_t L, int64_t C, int64_t mrs, int chunk, cudaStream_t st) {
+  const int64_t nvec = B * L * C / Vec<T>::N;
+  mod_gate_proj_kernel<T><<<(unsigned)((nvec + 255) / 256), 256, 0, st>>>(
+      static_cast<const T*>(r), static_cast<const T*>(mod), static_cast<const T*>(p),
+      static_cast<T*>(out), nvec, L, (int)C, mrs, chunk);
+}
+
+extern "C" int fluxb_modulation_gate_proj(const void* resid, const void* mod, const void* proj,
+                                          void* out, int64_t B, int64_t L, int64_t C,
+                                          int64_t mod_row_stride, int gate_chunk, int dtype,
+                                          fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "modulation_gate_proj: dtype %d", dtype);
+  if (B < 0 || L < 0 || C <= 0 || gate_chunk < 0) return set_error(FLUXB_ERR_BAD_ARG, "modulation_gate_proj: bad sizes");
+  if (B * L == 0) return FLUXB_OK;
+  const int vn = vec_elems(dtype);
+  if (!resid || !mod || !proj || !out || C % vn || mod_row_stride % vn || !aligned16(resid) ||
+      !aligned16(mod) || !aligned16(proj) || !aligned16(out))
+    return set_error(FLUXB_ERR_BAD_ARG, "modulation_gate_proj: null/misaligned pointer or C not a multiple of %d", vn);
+  if (mod_row_stride < (int64_t)(gate_chunk + 1) * C)
+    return set_error(FLUXB_ERR_BAD_ARG, "modulation_gate_proj: modulation row too short for chunk %d", gate_chunk);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FLUXB_BF16) launch_gate_proj<__nv_bfloat16>(resid, mod, proj, out, B, L, C, mod_row_stride, gate_chunk, st);
+  else launch_gate_proj<float>(resid, mod, proj, out, B, L, C, mod_row_stride, gate_chunk, st);
+  return launch_status("modulation_gate_proj");
+}
+
+extern "C" int fluxb_silu(const void* x, void* out, int64_t n, int dtype, fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16) return set_error(FLUXB_ERR_UNSUPPORTED, "silu: dtype %d", dtype);
+  if (n < 0) return set_error(FLUXB_ERR_BAD_ARG, "silu: negative size");
+  if (n == 0) return FLUXB_OK;
+  if (!x || !out || !aligned16(x) || !aligned16(out)) return set_error(FLUXB_ERR_BAD_ARG, "silu: null or misaligned pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int vn = vec_elems(dtype);
+  const int64_t nvec = (n + vn - 1) / vn;
+  const unsigned grid = (unsigned)((nvec + 255) / 256);
+  if (dtype == FLUXB_BF16)
+    silu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n);
+  else
+    silu_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(out), n);
+  return launch_status("silu");
+}
+
+extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void* bias, void* out,
+                                     int64_t B, int64_t N, int64_t K, int apply_silu,
+                                     fluxb_stream_t stream) {
+  if (B < 0 || N < 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: bad sizes");
+  if (B == 0 || N == 0) return FLUXB_OK;
+  if (!vec || !w || !out) return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: null pointer");
+  if (K % 8 || !aligned16(w) || !aligned16(vec))
+    return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: K must be a multiple of 8 and pointers 16-byte aligned");
+  if (K > 12288) return set_error(FLUXB_ERR_UNSUPPORTED, "modulation_gemv: K %lld > 12288", (long long)K);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(vec);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+  __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+  const unsigned grid = (unsigned)((N + 7) / 8 < 148 * 16 ? (N + 7) / 8 : 148 * 16);
+  int64_t b0 = 0;
+  while (b0 < B) {
+    const int64_t left = B - b0;
+    if (left >= 4) {
+      const size_t smem = (size_t)4 * K * sizeof(float);
+      cudaFuncSetAttribute(mod_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      mod_gemv_kernel<4><<<grid, 256, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
+      b0 += 4;
+    } else if (left >= 2) {
+      const size_t smem = (size_t)2 * K * sizeof(float);
+      cudaFuncSetAttribute(mod_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      mod_gemv_kernel<2><<<grid, 256, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
+      b0 += 2;
+    } else {
+      const size_t smem = (size_t)K * sizeof(float);
+      cudaFuncSetAttribute(mod_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      mod_gemv_kernel<1><<<grid, 256, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
+      b0 += 1;
+    }
+  }
+  return launch_status("modulation_gemv");
+}

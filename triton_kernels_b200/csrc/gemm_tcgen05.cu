@@ -1,0 +1,309 @@
+// y = x · w^T with fused epilogues, as a persistent, warp-specialised tcgen05 kernel.
+//
+//   warp 0      TMA producer: streams 128x64 tiles of x and 256x64 tiles of w (bf16, 128-byte
+//               swizzle) through a 4-stage shared-memory ring.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16) from shared
+//               memory into one of two 256-column fp32 accumulators in TMEM; tcgen05.commit
+//               releases ring slots and publishes finished accumulators.
+//   warps 2-5   epilogue: each warp reads its 32-lane TMEM quadrant with tcgen05.ld, applies
+//               bias / GELU / gate+residual in fp32 and stores bf16 rows with 16-byte stores.
+//               Because there are two accumulators the epilogue of tile i overlaps the main
+//               loop of tile i+1.
+//
+// Tiles are handed out statically (tile = blockIdx.x + i * gridDim.x) in an order that keeps
+// 8 row-blocks of x and a band of w resident in L2 at a time.  Edge tiles rely on TMA zero
+// fill for loads and on masks for stores.  Every barrier wait is bounded.
+#include "common.cuh"
+
+namespace fluxb {
+
+namespace gemm {
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct Params {
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* y;
+  __nv_bfloat16* y2;
+  const __nv_bfloat16* resid;
+  const __nv_bfloat16* gate;
+  int64_t ldy, ldy2, ldr, gate_stride, rows_per_batch;
+  int M, N, K;
+  int split, epi, epi2, round_before_act;
+  int tiles_m, tiles_n, num_tiles;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m_blk, int& n_blk) {
+  const int per_group = GROUP_M * p.tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(p.tiles_m - first_m, GROUP_M);
+  const int in_group = tile - group * per_group;
+  m_blk = first_m + in_group % gsize;
+  n_blk = in_group / gsize;
+}
+
+// Applies the epilogue to 32 consecutive columns of one output row held in registers.
+__device__ __forceinline__ void epilogue_chunk(const Params& p, const uint32_t (&acc)[32], int row,
+                                               int col0, bool second) {
+  const int epi = second ? p.epi2 : p.epi;
+  __nv_bfloat16* out = second ? p.y2 : p.y;
+  const int64_t ld = second ? p.ldy2 : p.ldy;
+  const int out_col0 = second ? col0 - p.split : col0;
+  const bool row_ok = row < p.M;
+  const int64_t b = (epi == FLUXB_EPI_GATE_RESID && row_ok) ? row / p.rows_per_batch : 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int col = col0 + j * 8;
+    if (col >= p.N) break;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(acc[j * 8 + e]);
+    if (p.bias != nullptr) {
+      const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+      v[0] += bf16_lo(bv.x); v[1] += bf16_hi(bv.x); v[2] += bf16_lo(bv.y); v[3] += bf16_hi(bv.y);
+      v[4] += bf16_lo(bv.z); v[5] += bf16_hi(bv.z); v[6] += bf16_lo(bv.w); v[7] += bf16_hi(bv.w);
+    }
+    if (epi == FLUXB_EPI_GELU) {
+      if (p.round_before_act) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(__float2bfloat16_rn(v[e]));
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+    } else if (epi == FLUXB_EPI_GATE_RESID) {
+      if (row_ok) {
+        const uint4 rv = *reinterpret_cast<const uint4*>(p.resid + (int64_t)row * p.ldr + col);
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(p.gate + b * p.gate_stride + col));
+        v[0] = bf16_lo(rv.x) + bf16_lo(gv.x) * v[0]; v[1] = bf16_hi(rv.x) + bf16_hi(gv.x) * v[1];
+        v[2] = bf16_lo(rv.y) + bf16_lo(gv.y) * v[2]; v[3] = bf16_hi(rv.y) + bf16_hi(gv.y) * v[3];
+        v[4] = bf16_lo(rv.z) + bf16_lo(gv.z) * v[4]; v[5] = bf16_hi(rv.z) + bf16_hi(gv.z) * v[5];
+        v[6] = bf16_lo(rv.w) + bf16_lo(gv.w) * v[6]; v[7] = bf16_hi(rv.w) + bf16_hi(gv.w) * v[7];
+      }
+    }
+    if (row_ok) {
+      uint4 o;
+      o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
+      o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+      *reinterpret_cast<uint4*>(out + (int64_t)row * ld + out_col0 + j * 8) = o;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(p, tile, m_blk, n_blk);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          uint8_t* a_dst = smem + stage * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(a_dst, &tm_a, &full_bar[stage], kb * BK, m_blk * BM);
+          tma_load_2d(b_dst, &tm_b, &full_bar[stage], kb * BK, n_blk * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(a_addr + A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 bf16 along K = 32 bytes = 2 descriptor address units
+            umma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m_blk * BM + quad * 32 + lane;
+      const int n0 = n_blk * BN;
+      const bool second = n0 >= p.split;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;  // uniform
+        uint32_t r[32];
+        tmem_ld_x32(t_addr + c * 32, r);
+        tmem_wait_ld();
+        epilogue_chunk(p, r, row, n0 + c * 32, second);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm
+}  // namespace fluxb
+
+using namespace fluxb;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void* y, int64_t M,
+                            int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int epi,
+                            void* y2, int64_t ldy2, int64_t split, int epi2, const void* resid,
+                            int64_t ldr, const void* gate, int64_t gate_stride,
+                            int64_t rows_per_batch, int round_before_act, fluxb_stream_t stream) {
+  using namespace fluxb::gemm;
+  if (M < 0 || N < 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: bad sizes");
+  if (M == 0 || N == 0) return FLUXB_OK;
+  if (M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "linear: dimension too large");
+  if (!x || !w || !y) return set_error(FLUXB_ERR_BAD_ARG, "linear: null pointer");
+  if (split < 0 || split > N) return set_error(FLUXB_ERR_BAD_ARG, "linear: split outside [0, N]");
+  if (split < N) {
+    if (!y2) return set_error(FLUXB_ERR_BAD_ARG, "linear: split < N needs a second output");
+    if (split % BN) return set_error(FLUXB_ERR_BAD_ARG, "linear: split must be a multiple of %d", BN);
+    if (ldy2 % 8 || !aligned16(y2)) return set_error(FLUXB_ERR_BAD_ARG, "linear: second output misaligned");
+  }
+  if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || ldy % 8 || ldx < K || ldw < K)
+    return set_error(FLUXB_ERR_BAD_ARG, "linear: K, N and row strides must be multiples of 8 (and strides >= K)");
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y) || !aligned16(bias))
+    return set_error(FLUXB_ERR_BAD_ARG, "linear: pointers must be 16-byte aligned");
+  const int epis[2] = {epi, split < N ? epi2 : FLUXB_EPI_NONE};
+  for (int e : epis) {
+    if (e != FLUXB_EPI_NONE && e != FLUXB_EPI_GELU && e != FLUXB_EPI_GATE_RESID)
+      return set_error(FLUXB_ERR_UNSUPPORTED, "linear: unknown epilogue %d", e);
+    if (e == FLUXB_EPI_GATE_RESID) {
+      if (!resid || !gate || rows_per_batch <= 0 || ldr % 8 || gate_stride % 8 || !aligned16(resid) ||
+          !aligned16(gate))
+        return set_error(FLUXB_ERR_BAD_ARG, "linear: gate/residual epilogue needs aligned resid, gate and rows_per_batch > 0");
+    }
+  }
+
+  CUtensorMap tm_a, tm_b;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[1] = {(uint64_t)ldx * 2};
+    const uint32_t box[2] = {BK, BM};
+    int rc = encode_tmap_bf16(&tm_a, x, 2, dims, strides, box);
+    if (rc != FLUXB_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t strides[1] = {(uint64_t)ldw * 2};
+    const uint32_t box[2] = {BK, BN};
+    int rc = encode_tmap_bf16(&tm_b, w, 2, dims, strides, box);
+    if (rc != FLUXB_OK) return rc;
+  }
+
+  Params p;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.y2 = static_cast<__nv_bfloat16*>(y2);
+  p.resid = static_cast<const __nv_bfloat16*>(resid);
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.ldy = ldy; p.ldy2 = ldy2; p.ldr = ldr; p.gate_stride = gate_stride;
+  p.rows_per_batch = rows_per_batch > 0 ? rows_per_batch : 1;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.split = (int)split; p.epi = epi; p.epi2 = epi2; p.round_before_act = round_before_act;
+  p.tiles_m = (int)((M + BM - 1) / BM);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.status = device_status_ptr();
+
+  {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
+  }
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: launch failed: %s", cudaGetErrorString(e));
+  return FLUXB_OK;
+}

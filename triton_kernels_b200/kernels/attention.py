@@ -1,0 +1,54 @@
+"""`scaled_dot_product_attention(q, k, v, sm_scale)` on the tcgen05 flash kernel
+(reference: triton_kernels/kernels/attention.py:173-221)."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from triton_kernels_b200 import _lib
+
+
+def attention_into(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, sm_scale: float) -> None:
+    """q,k,v,o are 4-D [B,H,L,D] *views* (any batch/head/row strides, unit stride on D)."""
+    B, H, Lq, D = q.shape
+    Lk = k.shape[2]
+    for t in (q, k, v, o):
+        assert t.stride(3) == 1
+    _lib.check(
+        _lib.load().fluxb_attention(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), B, H, Lq, Lk, D,
+            q.stride(0), q.stride(1), q.stride(2),
+            k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2),
+            o.stride(0), o.stride(1), o.stride(2),
+            float(sm_scale), _lib.stream_handle(),
+        )
+    )
+
+
+def scaled_dot_product_attention(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sm_scale: float | None = None
+) -> torch.Tensor:
+    """Non-causal softmax(q k^T * sm_scale) v for [B,H,L,D] bf16 tensors; returns [B,H,L,D].
+
+    Unlike the reference kernel, L need not be a multiple of the tile size (tails are masked).
+    """
+    HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert HEAD_DIM_Q == HEAD_DIM_K == HEAD_DIM_V
+    assert HEAD_DIM_K in {16, 32, 64, 128, 256}
+    _lib.require_cuda(q, k, v)
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise NotImplementedError("attention runs in bfloat16 only (the reference casts P to bf16 as well)")
+    if HEAD_DIM_K != 128:
+        raise NotImplementedError(f"attention is built for head_dim 128 (Flux); got {HEAD_DIM_K}")
+
+    def usable(t):
+        return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+
+    q, k, v = (t if usable(t) else t.contiguous() for t in (q, k, v))
+    if sm_scale is None:
+        sm_scale = 1 / math.sqrt(HEAD_DIM_K)
+    o = torch.empty(q.shape, device=q.device, dtype=q.dtype)
+    attention_into(q, k, v, o, sm_scale)
+    return o

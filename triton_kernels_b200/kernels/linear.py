@@ -1,0 +1,87 @@
+"""`linear(x, w, b, activation)` on the tcgen05 GEMM (reference: triton_kernels/kernels/linear.py:104-151)."""
+from __future__ import annotations
+
+import torch
+
+from triton_kernels_b200 import _lib
+
+
+class UnsupportedDtype(KeyError, TypeError):
+    """Raised for non-bf16 inputs.  The reference raises KeyError here (its tile-config table
+    has a bfloat16 entry only, triton_kernels/kernels/linear.py:105-114,142); this is also a
+    TypeError so callers can catch either."""
+
+
+def linear_into(
+    x2d: torch.Tensor,
+    w: torch.Tensor,
+    b: torch.Tensor | None,
+    y: torch.Tensor,
+    *,
+    epi: int = _lib.EPI_NONE,
+    y2: torch.Tensor | None = None,
+    split: int | None = None,
+    epi2: int = _lib.EPI_NONE,
+    resid: torch.Tensor | None = None,
+    gate: torch.Tensor | None = None,
+    gate_stride: int = 0,
+    rows_per_batch: int = 1,
+    round_before_act: bool = False,
+) -> None:
+    """Lowest-level launch: x2d [M,K] (row stride free), w [N,K], outputs caller-allocated 2-D
+    views (row stride free, unit column stride).  See fluxb_linear in include/fluxb200.h."""
+    M, K = x2d.shape
+    N = w.shape[0]
+    assert x2d.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1
+    if split is None:
+        split = N
+    _lib.check(
+        _lib.load().fluxb_linear(
+            _lib.ptr(x2d), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), M, N, K,
+            x2d.stride(0), w.stride(0), y.stride(0), epi,
+            _lib.ptr(y2), y2.stride(0) if y2 is not None else 0, split, epi2,
+            _lib.ptr(resid), resid.stride(0) if resid is not None else 0,
+            _lib.ptr(gate), gate_stride, rows_per_batch, int(round_before_act),
+            _lib.stream_handle(),
+        )
+    )
+
+
+def _as_2d(x: torch.Tensor, K: int) -> torch.Tensor:
+    x2d = x.reshape(-1, K)
+    if x2d.stride(1) != 1 or x2d.stride(0) % 8 or x2d.data_ptr() % 16:
+        x2d = x2d.contiguous()
+    return x2d
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, activation: str = "") -> torch.Tensor:
+    """y = x @ w.T (+ b), optionally followed by tanh-GELU; bf16 in/out, fp32 accumulation.
+
+    Same contract as the reference launcher: `w` is [N, K] (nn.Linear layout), any leading
+    dims on `x`, a fresh output tensor.  Bias add and GELU run in fp32 on the accumulator.
+    """
+    assert x.shape[-1] == w.shape[-1], "Incompatible dimensions"
+    assert x.dtype == w.dtype, "Incompatible dtypes"
+    assert activation in ("", "GELU"), f"unknown activation {activation!r}"
+    _lib.require_cuda(x, w, b)
+    if x.dtype != torch.bfloat16:
+        raise UnsupportedDtype(x.dtype)
+    N, K = w.shape
+    lead = x.shape[:-1]
+    x2d = _as_2d(x, K)
+    M = x2d.shape[0]
+    if w.stride(1) != 1 or w.stride(0) % 8:
+        w = w.contiguous()
+    if b is not None:
+        b = b.to(torch.bfloat16).contiguous()
+    y = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    if M <= 8 and K <= 12288 and K % 8 == 0 and x2d.is_contiguous() and w.is_contiguous() and not activation:
+        # Skinny problems (the modulation projection, M = batch) are pure weight streaming.
+        _lib.check(
+            _lib.load().fluxb_modulation_gemv(
+                _lib.ptr(x2d), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), M, N, K, 0, _lib.stream_handle()
+            )
+        )
+    else:
+        linear_into(x2d, w, b, y, epi=_lib.EPI_GELU if activation == "GELU" else _lib.EPI_NONE)
+    return y.reshape(*lead, N)
