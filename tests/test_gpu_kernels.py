@@ -1,0 +1,324 @@
+"""Per-kernel parity on a B200: every C-ABI kernel against the CPU oracle on identical seeded
+inputs.  Tolerances: fp32 I/O kernels 1e-5 absolute (the reference's own test tolerance);
+bf16 kernels atol = rtol = 2e-2 (the per-kernel tolerance of the benchmark spec)."""
+import math
+
+import pytest
+import torch
+
+from oracle import flux_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+BF = torch.bfloat16
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def close_bf16(got, want, atol=2e-2, rtol=2e-2):
+    torch.testing.assert_close(got.float().cpu(), want.float(), atol=atol, rtol=rtol)
+
+
+def rel_l2(got, want):
+    got, want = got.float().cpu(), want.float()
+    return float((got - want).norm() / want.norm())
+
+
+@pytest.fixture(scope="module")
+def tk(lib):
+    import triton_kernels_b200 as tk
+
+    assert torch.cuda.is_available()
+    return tk
+
+
+# ------------------------------------------------------------------ LayerNorm + modulation
+@pytest.mark.parametrize("B,L,N", [(1, 256, 1024), (2, 512, 2048), (16, 256, 3072), (3, 37, 3072), (2, 5, 72), (1, 9, 4096)])
+def test_layer_norm_modulation_fp32(tk, B, L, N):
+    g = gen(1)
+    x = torch.randn(B, L, N, generator=g) * 1.7 + 0.3
+    sc, sh = torch.randn(B, 1, N, generator=g), torch.randn(B, 1, N, generator=g)
+    y = tk.layer_norm_modulation(x.cuda(), sc.cuda(), sh.cuda())
+    torch.testing.assert_close(y.cpu(), O.layer_norm_modulation(x, sc, sh, eps=1e-5), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("B,L,N,eps", [(1, 4608, 3072, 1e-6), (2, 300, 3072, 1e-5), (4, 33, 256, 1e-6), (1, 7, 1000, 1e-6)])
+def test_layer_norm_modulation_bf16(tk, B, L, N, eps):
+    g = gen(2)
+    x = (torch.randn(B, L, N, generator=g) * 2 + 0.5).to(BF)
+    sc = (0.1 * torch.randn(B, 1, N, generator=g)).to(BF)
+    sh = (0.1 * torch.randn(B, 1, N, generator=g)).to(BF)
+    y = tk.layer_norm_modulation(x.cuda(), sc.cuda(), sh.cuda(), eps=eps)
+    assert y.dtype == BF
+    close_bf16(y, O.layer_norm_modulation(x.float(), sc.float(), sh.float(), eps=eps))
+
+
+def test_layer_norm_modulation_reads_packed_chunks_in_place(tk):
+    """scale/shift given as chunk views of a packed [B, 6C] tensor (no copies needed)."""
+    g = gen(3)
+    B, L, C = 2, 64, 3072
+    x = torch.randn(B, L, C, generator=g).to(BF)
+    mod = (0.2 * torch.randn(B, 6 * C, generator=g)).to(BF)
+    ch = mod[:, None, :].chunk(6, dim=-1)
+    mc = mod.cuda()
+    cc = mc[:, None, :].chunk(6, dim=-1)
+    y = tk.layer_norm_modulation(x.cuda(), cc[4], cc[3], eps=1e-6)
+    close_bf16(y, O.layer_norm_modulation(x.float(), ch[4].float(), ch[3].float(), eps=1e-6))
+
+
+# ------------------------------------------------------------------ RMSNorm
+@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 24, 512, 128), (8, 4, 77, 256), (1, 3, 50, 512), (2, 2, 9, 3072), (3, 1, 5, 96)])
+def test_rms_norm_fp32(tk, shape):
+    g = gen(4)
+    x = torch.randn(*shape, generator=g)
+    w = 1 + 0.1 * torch.randn(shape[-1], generator=g)
+    y = tk.rms_norm(x.cuda(), w.cuda())
+    torch.testing.assert_close(y.cpu(), O.rms_norm(x, w), atol=1e-5, rtol=1e-5)
+
+
+def test_rms_norm_bf16_on_head_split_view(tk):
+    """The block's use: q is a strided [B,H,L,D] view of the packed projection."""
+    g = gen(5)
+    B, L, H, D = 2, 333, 24, 128
+    qkv = torch.randn(B, L, 3 * H * D, generator=g).to(BF)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF)
+    q_view = qkv.cuda().view(B, L, 3, H, D).permute(2, 0, 3, 1, 4)[1]
+    y = tk.rms_norm(q_view, w.cuda())
+    want = O.rms_norm(qkv.view(B, L, 3, H, D).permute(2, 0, 3, 1, 4)[1].float(), w.float())
+    assert y.shape == (B, H, L, D) and y.is_contiguous()
+    close_bf16(y, want)
+
+
+def test_rms_norm_3072_wide_bf16(tk):
+    g = gen(6)
+    x = torch.randn(1, 4608, 3072, generator=g).to(BF)
+    w = (1 + 0.1 * torch.randn(3072, generator=g)).to(BF)
+    close_bf16(tk.rms_norm(x.cuda(), w.cuda()), O.rms_norm(x.float(), w.float()))
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 256, 128), (1, 24, 100, 128), (3, 2, 65, 256)])
+def test_rms_norm_backward_fp32(tk, shape):
+    g = gen(7)
+    x = torch.randn(*shape, generator=g)
+    w = 1 + 0.1 * torch.randn(shape[-1], generator=g)
+    dy = torch.randn(*shape, generator=g)
+    xc, wc = x.cuda().requires_grad_(), w.cuda().requires_grad_()
+    tk.rms_norm(xc, wc).backward(dy.cuda())
+    dx, dw = O.rms_norm_backward(dy.double(), x.double(), w.double())
+    torch.testing.assert_close(xc.grad.cpu().double(), dx, atol=1e-3, rtol=0)
+    torch.testing.assert_close(wc.grad.cpu().double(), dw, atol=1e-3, rtol=1e-4)
+
+
+# ------------------------------------------------------------------ RoPE
+@pytest.mark.parametrize("B,H,L,D", [(1, 2, 256, 128), (2, 24, 100, 128), (8, 3, 33, 256), (1, 5, 7, 64)])
+def test_rope_fp32_random_table(tk, B, H, L, D):
+    g = gen(8)
+    q, k = torch.randn(B, H, L, D, generator=g), torch.randn(B, H, L, D, generator=g)
+    pe = torch.randn(1, 1, L, D // 2, 2, 2, generator=g)
+    oq, ok = tk.apply_rope(q.cuda(), k.cuda(), pe.cuda())
+    wq, wk = O.apply_rope(q, k, pe)
+    torch.testing.assert_close(oq.cpu(), wq, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(ok.cpu(), wk, atol=1e-5, rtol=1e-5)
+
+
+def test_rope_bf16_flux_table(tk):
+    g = gen(9)
+    q, k = torch.randn(1, 24, 576, 128, generator=g).to(BF), torch.randn(1, 24, 576, 128, generator=g).to(BF)
+    pe = O.embed_nd(O.flux_position_ids(64, 16, 32), [16, 56, 56])
+    oq, ok = tk.apply_rope(q.cuda(), k.cuda(), pe.cuda())
+    wq, wk = O.apply_rope(q, k, pe)
+    # same fp32 math and one rounding on both sides: bit-exact up to fma contraction
+    close_bf16(oq, wq, atol=1e-2, rtol=1e-2)
+    close_bf16(ok, wk, atol=1e-2, rtol=1e-2)
+    assert (oq.cpu() != wq).float().mean() < 0.01
+
+
+def test_rope_rejects_batched_table(tk):
+    q = torch.randn(2, 2, 8, 128, device="cuda")
+    with pytest.raises(ValueError):
+        tk.apply_rope(q, q, torch.randn(2, 1, 8, 64, 2, 2, device="cuda"))
+
+
+# ------------------------------------------------------------------ q/k/v assembly, modulation ops, SiLU, GEMV
+def test_qkv_concat_is_a_pure_permutation(tk):
+    from triton_kernels_b200 import ops
+
+    g = gen(10)
+    B, H, D, Lt, Li = 2, 24, 128, 37, 150
+    txt = torch.randn(B, Lt, 3 * H * D, generator=g).to(BF)
+    img = torch.randn(B, Li, 3 * H * D, generator=g).to(BF)
+    q, k, v = ops.qkv_concat(txt.cuda(), img.cuda(), H)
+    wq, wk, wv = O.qkv_concat(txt, img, H)
+    assert torch.equal(q.cpu(), wq) and torch.equal(k.cpu(), wk) and torch.equal(v.cpu(), wv)
+
+
+def test_qkv_prepare_with_norm_and_rope(tk):
+    from triton_kernels_b200 import ops
+
+    g = gen(11)
+    B, H, D, Lt, Li = 1, 24, 128, 64, 16 * 24
+    txt = torch.randn(B, Lt, 3 * H * D, generator=g).to(BF)
+    img = torch.randn(B, Li, 3 * H * D, generator=g).to(BF)
+    scales = [(1 + 0.1 * torch.randn(D, generator=g)).to(BF) for _ in range(4)]
+    pe = O.embed_nd(O.flux_position_ids(Lt, 16, 24), [16, 56, 56])
+    q, k, v = ops.qkv_prepare([txt.cuda(), img.cuda()], H, [scales[0].cuda(), scales[2].cuda()],
+                              [scales[1].cuda(), scales[3].cuda()], pe.cuda())
+    tq, tk_, tv = O.split_heads(txt.float(), H)
+    iq, ik, iv = O.split_heads(img.float(), H)
+    wq = torch.cat((O.rms_norm(tq, scales[0].float()), O.rms_norm(iq, scales[2].float())), 2)
+    wk = torch.cat((O.rms_norm(tk_, scales[1].float()), O.rms_norm(ik, scales[3].float())), 2)
+    wq, wk = O.apply_rope(wq, wk, pe)
+    close_bf16(q, wq)
+    close_bf16(k, wk)
+    assert torch.equal(v.cpu().float(), torch.cat((tv, iv), 2))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_modulation_ops_and_silu(tk, dtype):
+    from triton_kernels_b200 import ops
+
+    g = gen(12)
+    B, L, C = 2, 50, 3072
+    x = torch.randn(B, L, C, generator=g).to(dtype)
+    proj = torch.randn(B, L, C, generator=g).to(dtype)
+    mod = torch.randn(B, 6 * C, generator=g).to(dtype)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    for is1 in (True, False):
+        got = ops.modulation_scale_shift(x.cuda(), mod.cuda(), is1)
+        torch.testing.assert_close(got.float().cpu(), O.modulation_scale_shift(x.float(), mod.float(), is1), **tol)
+    for chunk in (2, 5):
+        got = ops.modulation_gate_proj(x.cuda(), mod.cuda(), proj.cuda(), chunk)
+        torch.testing.assert_close(got.float().cpu(), O.modulation_gate_proj(x.float(), mod.float(), proj.float(), chunk), **tol)
+    v = torch.randn(3, 1001, generator=g).to(dtype) * 3
+    torch.testing.assert_close(ops.silu(v.cuda()).float().cpu(), O.silu(v.float()), **tol)
+
+
+@pytest.mark.parametrize("B,N,K", [(1, 18432, 3072), (2, 9216, 3072), (5, 1000, 256), (8, 64, 3072)])
+def test_modulation_projection(tk, B, N, K):
+    from triton_kernels_b200 import ops
+
+    g = gen(13)
+    vec = torch.randn(B, K, generator=g).to(BF)
+    w = (0.02 * torch.randn(N, K, generator=g)).to(BF)
+    b = (0.02 * torch.randn(N, generator=g)).to(BF)
+    got = ops.modulation_silu_linear(vec.cuda(), w.cuda(), b.cuda())
+    want = O.linear(O.silu(vec.float()), w.float(), b.float())
+    close_bf16(got, want)
+
+
+# ------------------------------------------------------------------ linear (tcgen05 GEMM)
+@pytest.mark.parametrize(
+    "M,K,N,act,bias",
+    [
+        (128, 64, 256, "", False),       # exactly one tile, one k-block
+        (128, 256, 256, "", True),       # ring wraps once
+        (256, 1024, 1024, "", True),
+        (1024, 512, 3072, "GELU", True),
+        (300, 328, 1000, "", True),      # ragged M, K, N
+        (77, 64, 64, "GELU", True),      # smaller than one tile in every dim
+        (4608, 3072, 3072, "", True),    # multiple tiles per CTA (persistent loop + both accumulators)
+    ],
+)
+def test_linear(tk, M, K, N, act, bias):
+    g = gen(14)
+    x = torch.randn(M, K, generator=g).to(BF)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(BF)
+    b = (0.5 * torch.randn(N, generator=g)).to(BF) if bias else None
+    y = tk.linear(x.cuda(), w.cuda(), b.cuda() if bias else None, activation=act)
+    want = O.linear(x.double(), w.double(), b.double() if bias else None, act)
+    close_bf16(y, want)
+    assert rel_l2(y, want) < 4e-3
+
+
+def test_linear_batched_input_and_small_m(tk):
+    g = gen(15)
+    x = torch.randn(2, 3, 50, 256, generator=g).to(BF)
+    w = (0.05 * torch.randn(512, 256, generator=g)).to(BF)
+    y = tk.linear(x.cuda(), w.cuda(), None)
+    assert y.shape == (2, 3, 50, 512)
+    close_bf16(y, O.linear(x.float(), w.float()))
+    v = torch.randn(2, 3072, generator=g).to(BF)
+    w2 = (0.02 * torch.randn(1024, 3072, generator=g)).to(BF)
+    close_bf16(tk.linear(v.cuda(), w2.cuda(), None), O.linear(v.float(), w2.float()))
+
+
+def test_linear_rejects_fp32_like_the_reference(tk):
+    with pytest.raises(KeyError):
+        tk.linear(torch.randn(8, 64, device="cuda"), torch.randn(64, 64, device="cuda"), None)
+
+
+def test_linear_epilogues(tk):
+    """Column-split output with GELU on the second part, and the gate/residual epilogue."""
+    from triton_kernels_b200 import _lib
+    from triton_kernels_b200.kernels.linear import linear_into
+
+    g = gen(16)
+    M, K, N, split = 200, 256, 768, 512
+    x = torch.randn(M, K, generator=g).to(BF)
+    w = (torch.randn(N, K, generator=g) / 16).to(BF)
+    b = (0.1 * torch.randn(N, generator=g)).to(BF)
+    y1 = torch.zeros(M, split, dtype=BF, device="cuda")
+    wide = torch.zeros(M, 64 + (N - split), dtype=BF, device="cuda")
+    linear_into(x.cuda(), w.cuda(), b.cuda(), y1, y2=wide[:, 64:], split=split, epi2=_lib.EPI_GELU)
+    ref = O.linear(x.float(), w.float(), b.float())
+    close_bf16(y1, ref[:, :split])
+    close_bf16(wide[:, 64:], O.gelu_tanh(ref[:, split:]))
+    assert float(wide[:, :64].abs().max()) == 0.0  # untouched columns
+
+    B, L = 2, 100
+    resid = torch.randn(B * L, N, generator=g).to(BF)
+    gate = torch.randn(B, N, generator=g).to(BF)
+    out = torch.empty(B * L, N, dtype=BF, device="cuda")
+    gc = gate.cuda()
+    linear_into(x.cuda(), w.cuda(), b.cuda(), out, epi=_lib.EPI_GATE_RESID, resid=resid.cuda(), gate=gc,
+                gate_stride=gc.stride(0), rows_per_batch=L)
+    want = resid.float() + gate.float().repeat_interleave(L, 0) * ref
+    close_bf16(out, want)
+
+
+# ------------------------------------------------------------------ attention
+@pytest.mark.parametrize("B,H,L", [(1, 2, 256), (2, 4, 512), (1, 24, 1024), (1, 3, 128), (2, 2, 200), (1, 2, 77), (1, 1, 1), (1, 2, 641)])
+def test_attention(tk, B, H, L):
+    g = gen(17)
+    q, k, v = (torch.randn(B, H, L, 128, generator=g).to(BF) for _ in range(3))
+    o = tk.scaled_dot_product_attention(q.cuda(), k.cuda(), v.cuda())
+    want = O.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    torch.testing.assert_close(o.float().cpu(), want, atol=1e-2, rtol=2e-2)
+    assert rel_l2(o, want) < 1e-2
+
+
+def test_attention_sharp_softmax_and_custom_scale(tk):
+    """Large logits make the running maximum jump, exercising the lazy-rescale path."""
+    g = gen(18)
+    B, H, L = 1, 2, 1152
+    q = (4 * torch.randn(B, H, L, 128, generator=g)).to(BF)
+    k = (4 * torch.randn(B, H, L, 128, generator=g)).to(BF)
+    v = torch.randn(B, H, L, 128, generator=g).to(BF)
+    for scale in (None, 0.3):
+        o = tk.scaled_dot_product_attention(q.cuda(), k.cuda(), v.cuda(), sm_scale=scale)
+        want = O.scaled_dot_product_attention(q.float(), k.float(), v.float(), scale)
+        torch.testing.assert_close(o.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_attention_different_kv_length_and_strided_output(tk):
+    from triton_kernels_b200.kernels.attention import attention_into
+
+    g = gen(19)
+    B, H, Lq, Lk, D = 2, 3, 300, 450, 128
+    q = torch.randn(B, H, Lq, D, generator=g).to(BF)
+    k = torch.randn(B, H, Lk, D, generator=g).to(BF)
+    v = torch.randn(B, H, Lk, D, generator=g).to(BF)
+    out = torch.zeros(B, Lq, H * D + 256, dtype=BF, device="cuda")  # wider buffer, like the single block's
+    o_view = out[:, :, : H * D].unflatten(2, (H, D)).permute(0, 2, 1, 3)
+    attention_into(q.cuda(), k.cuda(), v.cuda(), o_view, D**-0.5)
+    want = O.scaled_dot_product_attention(q.float(), k.float(), v.float()).permute(0, 2, 1, 3).reshape(B, Lq, H * D)
+    torch.testing.assert_close(out[:, :, : H * D].float().cpu(), want, atol=1e-2, rtol=2e-2)
+    assert float(out[:, :, H * D :].abs().max()) == 0.0
+
+
+def test_device_status_is_clean(tk):
+    from triton_kernels_b200 import _lib
+
+    assert _lib.device_status() == (0, 0)
