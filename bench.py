@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the Flux double-stream block forward (bf16, 4096 image + 512 text tokens).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one forward pass of one DoubleStreamBlock (hidden 3072, 24 heads, MLP 12288) over
+one image's 4608 tokens.  With N > 1 (launched by torch.distributed.run, one rank per GPU) each
+rank runs its own image through a replica of the block: batch data-parallel, no collective on
+the data path, weak scaling.  Rank 0 prints one JSON line.
+
+  value     tokens/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e       tokens/s through the public module call with HOST inputs/outputs: pinned-host ->
+            device copies of img/txt/vec and a device -> host copy of both outputs every step,
+            pipelined over three streams
+  roofline  the largest GEMM of the step (MLP up-projection of the image stream, M=4096,
+            K=3072, N=12288, GELU epilogue) timed per launch with CUDA events inside real steps,
+            against the measured bf16 peak in MEASURED_PEAKS.json
+  cpu_baseline  the CPU oracle (PyTorch fp32 restatement of the reference's block) on the
+            host cores, on a bounded sample
+
+`--impl reference` times that CPU path alone (rank 0 only) and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "flux_double_block_fwd_tokens_per_s"
+UNIT = "tokens/s"
+C, H, MLP_RATIO = 3072, 24, 4.0
+L_IMG, L_TXT = 4096, 512
+GRID = 64
+SEED = 2
+TOKENS = L_IMG + L_TXT
+WORKLOAD = (f"flux_double_stream_block hidden {C}, {H} heads x 128, {L_IMG} image + {L_TXT} text tokens, "
+            "batch 1 per GPU, weights N(0,0.02), seed 2")
+# Algorithmic work of the timed GEMM (2*M*N*K) and of one block step.
+DOM_M, DOM_K, DOM_N = L_IMG, C, int(C * MLP_RATIO)
+BLOCK_FLOP = 2 * TOKENS * C * (3 * C + C + 2 * int(C * MLP_RATIO)) + 4 * H * TOKENS * TOKENS * (C // H)
+NCU_TRAFFIC_BYTES = None  # dram read+write bytes per launch of the timed GEMM, from profiles/
+
+
+def make_inputs(seed: int, l_img: int = L_IMG, l_txt: int = L_TXT, grid: int = GRID):
+    """Seeded fp32 parameters and activations of the double-stream block config (CPU)."""
+    from oracle import flux_oracle as O
+
+    g = torch.Generator().manual_seed(seed)
+    params = O.init_params(O.double_block_shapes(C, MLP_RATIO), g)
+    img = torch.randn(1, l_img, C, generator=g)
+    txt = torch.randn(1, l_txt, C, generator=g)
+    vec = torch.randn(1, C, generator=g)
+    pe = O.embed_nd(O.flux_position_ids(l_txt, l_img // grid, grid), [16, 56, 56])
+    return params, img, txt, vec, pe
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while a region runs."""
+
+    FIELDS = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+        "clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = [s for s, p in zip(sm, power) if p > 300] or sm
+        return {
+            "sm_mhz": statistics.median(busy) if busy else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "power_w_max": max(power) if power else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def cpu_block_time(tokens_img: int, tokens_txt: int, runs: int, warm: int = 1):
+    """Seconds per forward of the CPU oracle's double-stream block (fp32, all host threads)."""
+    from oracle import flux_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    params, img, txt, vec, pe = make_inputs(SEED, tokens_img, tokens_txt, GRID)
+    times = []
+    with torch.no_grad():
+        for i in range(warm + runs):
+            t0 = time.perf_counter()
+            O.double_stream_block(img, txt, vec, pe, params, H)
+            if i >= warm:
+                times.append(time.perf_counter() - t0)
+    return statistics.median(times), torch.get_num_threads()
+
+
+def run_reference(args, rank: int):
+    """The reference's own CPU path for the block (its PyTorch blocks, restated in oracle/),
+    timed on the host cores; every step is one forward over a bounded token sample."""
+    if rank != 0:
+        return
+    from oracle import flux_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    budget_s = 150.0
+    sizes = [(L_IMG, L_TXT), (1024, 128), (256, 64)]
+    chosen = sizes[-1]
+    per = None
+    for li, lt in sizes:
+        t, _ = cpu_block_time(li, lt, runs=1, warm=0)
+        if t * (args.steps + args.warmup) <= budget_s:
+            chosen, per = (li, lt), t
+            break
+    li, lt = chosen
+    params, img, txt, vec, pe = make_inputs(SEED, li, lt, GRID)
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            O.double_stream_block(img, txt, vec, pe, params, H)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            O.double_stream_block(img, txt, vec, pe, params, H)
+        dt = time.perf_counter() - t0
+    value = (li + lt) * args.steps / dt
+    sample = f"{args.steps} forward passes of the double-stream block over {li}+{lt} tokens (fp32, torch CPU)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sampled_tokens_per_step": li + lt},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the B200 kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import triton_kernels_b200 as tk
+    from triton_kernels_b200 import _lib
+    import triton_kernels_b200.kernels.linear  # noqa: F401
+
+    linear_mod = sys.modules["triton_kernels_b200.kernels.linear"]  # the module, not the function of that name
+
+    _lib.load()
+    BF = torch.bfloat16
+    params, img, txt, vec, pe = make_inputs(SEED + rank)  # each rank has its own image
+    block = tk.DoubleStreamBlock(C, H, MLP_RATIO).to(BF)
+    block.load_state_dict({k: v.to(BF) for k, v in params.items()})
+    block = block.to(dev)
+    img_h, txt_h, vec_h = (t.to(BF).pin_memory() for t in (img, txt, vec))
+    img_d, txt_d, vec_d, pe_d = img_h.to(dev), txt_h.to(dev), vec_h.to(dev), pe.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- device-resident timing
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            block(img_d, txt_d, vec_d, pe_d)
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        barrier()
+        calls0 = _lib.kernel_calls
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            block(img_d, txt_d, vec_d, pe_d)
+        e1.record()
+        barrier()
+        launches = _lib.kernel_calls - calls0
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        clocks = sampler.stop()
+
+        # ------------------------------------------------------------ dominant kernel, per launch
+        linear_mod.launch_probe = []
+        for _ in range(min(args.steps, 20)):
+            block(img_d, txt_d, vec_d, pe_d)
+        torch.cuda.synchronize()
+        durs = [a.elapsed_time(b) for (m, n, k, a, b) in linear_mod.launch_probe if (m, n, k) == (DOM_M, DOM_N, DOM_K)]
+        linear_mod.launch_probe = None
+        dom_ms = sum(durs) / len(durs)
+
+        # ------------------------------------------------------------ end to end with host buffers
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        s_cmp = torch.cuda.current_stream()
+        bufs = [[torch.empty_like(img_d), torch.empty_like(txt_d), torch.empty_like(vec_d)] for _ in range(2)]
+        outs_h = [[torch.empty_like(img_h).pin_memory(), torch.empty_like(txt_h).pin_memory()] for _ in range(2)]
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [torch.cuda.Event() for _ in range(2)]
+        out_ready = [torch.cuda.Event() for _ in range(2)]
+
+        def e2e_steps(n):
+            keep = []
+            for i in range(n):
+                b = i & 1
+                with torch.cuda.stream(s_in):
+                    s_in.wait_event(in_free[b])
+                    for dst, src in zip(bufs[b], (img_h, txt_h, vec_h)):
+                        dst.copy_(src, non_blocking=True)
+                    in_ready[b].record(s_in)
+                s_cmp.wait_event(in_ready[b])
+                oi, ot = block(bufs[b][0], bufs[b][1], bufs[b][2], pe_d)
+                in_free[b].record(s_cmp)
+                out_ready[b].record(s_cmp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(out_ready[b])
+                    outs_h[b][0].copy_(oi, non_blocking=True)
+                    outs_h[b][1].copy_(ot, non_blocking=True)
+                    oi.record_stream(s_out)
+                    ot.record_stream(s_out)
+                keep.append((oi, ot))
+                if len(keep) > 2:
+                    keep.pop(0)
+            s_cmp.wait_stream(s_out)
+
+        for ev in in_free:
+            ev.record(s_cmp)
+        e2e_steps(args.warmup)
+        barrier()
+        t0 = time.perf_counter()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        e2e_steps(args.steps)
+        g1.record()
+        barrier()
+        e2e_ms = max_over_ranks(max(g0.elapsed_time(g1), 0.0))
+        e2e_wall_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+
+    code, where = _lib.device_status()
+    if code != 0:
+        raise SystemExit(f"device status word reports error {code} at {where}")
+
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peak, peak_src = json.loads(peaks_path.read_text())["bf16_tflops"], "measured (burst)"
+    else:
+        peak, peak_src = 1590.0, "fallback"
+    dom_flop = 2.0 * DOM_M * DOM_N * DOM_K
+    achieved = dom_flop / (dom_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        value = world * TOKENS * args.steps / (ms * 1e-3)
+        e2e_value = world * TOKENS * args.steps / (e2e_ms * 1e-3)
+        h2d = sum(t.numel() * t.element_size() for t in (img_h, txt_h, vec_h))
+        d2h = sum(t.numel() * t.element_size() for t in (img_h, txt_h))
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": WORKLOAD,
+                "parallelism": f"batch data-parallel x{world}" if world > 1 else "single GPU",
+                "l2": "no flush: 0.68 GB of weights + 0.3 GB of activations per step exceed the 126 MB L2",
+                "block_tflop": BLOCK_FLOP / 1e12,
+                "block_tflops_achieved": BLOCK_FLOP * args.steps / (ms * 1e-3) / 1e12,
+            },
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps, "wall_ms_per_step": e2e_wall_ms / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {
+                "bound": "tensor", "kernel": f"gemm_kernel M={DOM_M} K={DOM_K} N={DOM_N} +bias+GELU",
+                "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "TFLOP/s",
+                "frac": achieved / peak, "launch_ms": dom_ms, "traffic": NCU_TRAFFIC_BYTES,
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            t, threads = cpu_block_time(L_IMG, L_TXT, runs=3, warm=1)
+            line["cpu_baseline"] = {
+                "value": TOKENS / t, "unit": UNIT, "cores": threads, "kind": "port",
+                "sample": f"3 forward passes of the same double-stream block ({L_IMG}+{L_TXT} tokens, fp32, torch CPU)",
+            }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -39,6 +39,7 @@ SIGNATURES = {
 }
 
 _lib = None
+kernel_calls = 0  # C-ABI compute calls that returned success (each launches at least one kernel)
 
 
 class FluxbError(RuntimeError):
@@ -65,7 +66,9 @@ def load() -> ctypes.CDLL:
 
 def check(rc: int) -> None:
     """Turns a status code into the Python exception the reference API would raise."""
+    global kernel_calls
     if rc == 0:
+        kernel_calls += 1
         return
     msg = load().fluxb_last_error().decode()
     if rc == ERR_BAD_ARG:

@@ -13,6 +13,8 @@
 // Tiles are handed out statically (tile = blockIdx.x + i * gridDim.x) in an order that keeps
 // 8 row-blocks of x and a band of w resident in L2 at a time.  Edge tiles rely on TMA zero
 // fill for loads and on masks for stores.  Every barrier wait is bounded.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace fluxb {
@@ -40,6 +42,7 @@ struct Params {
   int M, N, K;
   int split, epi, epi2, round_before_act;
   int tiles_m, tiles_n, num_tiles;
+  int pair_stages;  // CTA-pair kernel: ring depth in use (<= gemm2::STAGES)
   DeviceStatus* status;
 };
 
@@ -228,6 +231,184 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 }
 
 }  // namespace gemm
+
+// ----------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster share one 256x256 output tile.  Each CTA loads its
+// own 128 rows of x and only HALF of the w tile (128 rows); one thread of the even ("leader")
+// CTA issues cta_group::2 MMAs (M=256, N=256, K=16) that run on both SMs, each tensor core
+// reading the other half of w from its partner's shared memory.  Per SM this halves the
+// shared-memory and L2 traffic for w, which is what bounds the single-CTA kernel.
+//   - both CTAs' TMA loads count on the leader's "full" barrier (pair form of the bulk copy)
+//   - slot release and accumulator-full are tcgen05.commit arrivals delivered to the barrier
+//     at the same offset in BOTH CTAs, so each CTA's producer / epilogue waits locally
+//   - accumulator-empty is counted on the leader (4 epilogue warps x 2 CTAs, remote arrive)
+// (Relaying the slot release through the leader's producer with a remote mbarrier arrive
+// instead was measured at half the throughput.)
+// ----------------------------------------------------------------------------------------
+namespace gemm2 {
+using gemm::Params;
+using gemm::epilogue_chunk;
+constexpr int BM = 128;       // rows of x per CTA (256 per pair)
+constexpr int BN = 256;       // output columns per tile
+constexpr int BNH = 128;      // rows of w loaded by each CTA
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BNH * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 4;    // in 256-row blocks
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int tiles_m, int& m_blk, int& n_blk) {
+  const int per_group = GROUP_M * p.tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(tiles_m - first_m, GROUP_M);
+  const int in_group = tile - group * per_group;
+  m_blk = first_m + in_group % gsize;
+  n_blk = in_group / gsize;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int num_tiles = tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // partner's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+        int m_blk, n_blk;
+        tile_coords(p, tile, tiles_m, m_blk, n_blk);
+        const int row0 = m_blk * 2 * BM + (int)rank * BM;
+        const int col0 = n_blk * BN + (int)rank * BNH;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 41)) { ok = false; break; }
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          const uint32_t full_addr = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          uint8_t* a_dst = smem + stage * STAGE_BYTES;
+          tma_load_2d_pair(a_dst, &tm_a, full_addr, kb * BK, row0);
+          tma_load_2d_pair(a_dst + A_BYTES, &tm_b, full_addr, kb * BK, col0);
+          if (++stage == p.pair_stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 43)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag, p.status, 44)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(a_addr + A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair_both(&empty_bar[stage]);
+          if (++stage == p.pair_stages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair_both(&acc_full[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quad = warp & 3;
+    int local = 0;
+    bool ok = true;
+    const uint32_t acc_empty_leader0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+    for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, tiles_m, m_blk, n_blk);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, p.status, 45)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m_blk * 2 * BM + (int)rank * BM + quad * 32 + lane;
+      const int n0 = n_blk * BN;
+      const bool second = n0 >= p.split;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (n0 + c * 32 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_x32(t_addr + c * 32, r);
+        tmem_wait_ld();
+        epilogue_chunk(p, r, row, n0 + c * 32, second);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader0 + acc * 8);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while its partner may still touch its memory
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm2
 }  // namespace fluxb
 
 using namespace fluxb;
@@ -266,6 +447,13 @@ extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void
     }
   }
 
+  // Kernel choice: CTA pairs (256x256 tiles) unless FLUXB_GEMM_PAIR=0 asks for the single-CTA kernel.
+  static const int pair_env = [] {
+    const char* s = getenv("FLUXB_GEMM_PAIR");
+    return (s != nullptr && *s != 0) ? atoi(s) : 1;
+  }();
+  const bool use_pair = pair_env != 0;
+
   CUtensorMap tm_a, tm_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
@@ -277,7 +465,7 @@ extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
     const uint64_t strides[1] = {(uint64_t)ldw * 2};
-    const uint32_t box[2] = {BK, BN};
+    const uint32_t box[2] = {BK, (uint32_t)(use_pair ? fluxb::gemm2::BNH : BN)};
     int rc = encode_tmap_bf16(&tm_b, w, 2, dims, strides, box);
     if (rc != FLUXB_OK) return rc;
   }
@@ -296,13 +484,23 @@ extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.status = device_status_ptr();
+  static const int stages_env = [] { const char* s = getenv("FLUXB_GEMM_PAIR_STAGES"); return (s && *s) ? atoi(s) : fluxb::gemm2::STAGES; }();
+  p.pair_stages = stages_env < 2 ? 2 : (stages_env > fluxb::gemm2::STAGES ? fluxb::gemm2::STAGES : stages_env);
 
-  {
+  if (use_pair) {
+    cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         fluxb::gemm2::SMEM_BYTES);
+    if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
+    const int tiles = (int)((M + 255) / 256) * p.tiles_n;
+    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    fluxb::gemm2::gemm_pair_kernel<<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES,
+                                     static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+  } else {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
+    const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+    gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
   }
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-  gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;

@@ -12,6 +12,10 @@ class UnsupportedDtype(KeyError, TypeError):
     TypeError so callers can catch either."""
 
 
+# Benchmarks set this to a list to collect (M, N, K, start_event, end_event) per GEMM launch.
+launch_probe: list | None = None
+
+
 def linear_into(
     x2d: torch.Tensor,
     w: torch.Tensor,
@@ -35,6 +39,9 @@ def linear_into(
     assert x2d.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1
     if split is None:
         split = N
+    if launch_probe is not None:
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev0.record()
     _lib.check(
         _lib.load().fluxb_linear(
             _lib.ptr(x2d), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), M, N, K,
@@ -45,6 +52,10 @@ def linear_into(
             _lib.stream_handle(),
         )
     )
+    if launch_probe is not None:
+        ev1 = torch.cuda.Event(enable_timing=True)
+        ev1.record()
+        launch_probe.append((M, N, K, ev0, ev1))
 
 
 def _as_2d(x: torch.Tensor, K: int) -> torch.Tensor:
