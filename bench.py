@@ -183,6 +183,113 @@ def run_reference(args, rank: int):
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------------------
+# Per-kernel microbenchmarks at the shapes of the benchmark's kernel config (seed 1):
+# (a) RMSNorm [1,4608,3072] and per-head [1,24,4608,128]; (b) LayerNorm+modulation
+# [1,4608,3072]; (c) RoPE on q,k [1,24,4608,128]; (d) linear+bias+GELU M=4608 K=3072 N=12288;
+# (e) attention [1,24,4608,128]; plus the fused q/k/v assembly and the modulation projection.
+# Each kernel is launched back to back over rotating buffer sets that together exceed the
+# 126 MB L2, and timed with CUDA events; one JSON line per kernel.
+# --------------------------------------------------------------------------------------
+def run_micro(which: str, steps: int, warmup: int):
+    import triton_kernels_b200  # noqa: F401
+    from triton_kernels_b200 import _lib
+    from triton_kernels_b200.kernels.attention import attention_into
+    from triton_kernels_b200.kernels.linear import linear_into
+    from triton_kernels_b200.kernels.normalization import layer_norm_modulation_into
+    from triton_kernels_b200.ops.fused import qkv_prepare_into
+
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    BF = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(1)
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {
+        "hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    L, Cc, Hh, D = TOKENS, C, H, C // H
+    st = _lib.stream_handle()
+
+    def randn(*shape, std=1.0):
+        return (torch.randn(*shape, device=dev, generator=g) * std).to(BF)
+
+    def time_calls(calls):
+        for i in range(max(warmup, 1) * len(calls)):
+            calls[i % len(calls)]()
+        torch.cuda.synchronize()
+        n = max(steps, 1) * len(calls)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(n):
+            calls[i % len(calls)]()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e-3 / n  # seconds per launch
+
+    def sets_for(bytes_per_set):
+        return max(2, int(300e6 // bytes_per_set) + 1)
+
+    def emit(name, sec, work, bound):
+        if bound == "hbm":
+            ach, peak, unit = work / sec / 1e9, peaks["hbm_gbs"], "GB/s"
+        else:
+            ach, peak, unit = work / sec / 1e12, peaks["bf16_tflops"], "TFLOP/s"
+        print(json.dumps({"micro": name, "us_per_launch": sec * 1e6, "bound": bound, "achieved": ach, "peak": peak,
+                          "unit": unit, "frac": ach / peak, "algorithmic_work": work}), flush=True)
+
+    def want(name):
+        return which in ("all", name)
+
+    if want("layer_norm_modulation"):
+        sc, sh = randn(1, Cc, std=0.1), randn(1, Cc, std=0.1)
+        bufs = [(randn(L, Cc), torch.empty(L, Cc, device=dev, dtype=BF)) for _ in range(sets_for(2 * L * Cc * 2))]
+        calls = [lambda x=x, y=y: layer_norm_modulation_into(x, sc, sh, y, L, 1e-6) for x, y in bufs]
+        emit("layer_norm_modulation[1,4608,3072]", time_calls(calls), 2 * L * Cc * 2 + 2 * Cc * 2, "hbm")
+    if want("rms_norm"):
+        w = torch.ones(Cc, device=dev, dtype=BF)
+        bufs = [(randn(L, Cc), torch.empty(L, Cc, device=dev, dtype=BF)) for _ in range(sets_for(2 * L * Cc * 2))]
+        calls = [lambda x=x, y=y: lib.fluxb_rms_norm(x.data_ptr(), w.data_ptr(), y.data_ptr(), None, 1, 1, L, Cc, 0, 0, Cc,
+                                                      1e-6, 1, st) for x, y in bufs]
+        emit("rms_norm[1,4608,3072]", time_calls(calls), 2 * L * Cc * 2, "hbm")
+        wh = torch.ones(D, device=dev, dtype=BF)
+        calls = [lambda x=x, y=y: lib.fluxb_rms_norm(x.data_ptr(), wh.data_ptr(), y.data_ptr(), None, 1, 1, L * Hh, D, 0, 0,
+                                                      D, 1e-6, 1, st) for x, y in bufs]
+        emit("rms_norm[1,24,4608,128]", time_calls(calls), 2 * L * Cc * 2, "hbm")
+    pe = torch.randn(L, D // 2, 2, 2, device=dev, generator=g)
+    if want("rope"):
+        bufs = [tuple(randn(Hh, L, D) for _ in range(2)) + tuple(torch.empty(Hh, L, D, device=dev, dtype=BF) for _ in range(2))
+                for _ in range(sets_for(4 * L * Cc * 2))]
+        calls = [lambda q=q, k=k, oq=oq, ok=ok: lib.fluxb_rope(q.data_ptr(), k.data_ptr(), pe.data_ptr(), oq.data_ptr(),
+                                                                 ok.data_ptr(), Hh, L, D, 1, st) for q, k, oq, ok in bufs]
+        emit("rope[1,24,4608,128]", time_calls(calls), 4 * L * Cc * 2 + pe.numel() * 4, "hbm")
+    if want("qkv_prepare"):
+        wh = torch.ones(D, device=dev, dtype=BF)
+        bufs = [(randn(1, L, 3 * Cc),) + tuple(torch.empty(1, Hh, L, D, device=dev, dtype=BF) for _ in range(3))
+                for _ in range(sets_for(6 * L * Cc * 2))]
+        calls = [lambda s_=s_, q=q, k=k, v=v: qkv_prepare_into([(s_, wh, wh)], pe, q, k, v, Hh) for s_, q, k, v in bufs]
+        emit("qkv_prepare[1,4608,9216]", time_calls(calls), 6 * L * Cc * 2 + pe.numel() * 4, "hbm")
+    if want("modulation_projection"):
+        vec = randn(1, Cc)
+        bufs = [(randn(6 * Cc, Cc, std=0.02), randn(6 * Cc, std=0.02), torch.empty(1, 6 * Cc, device=dev, dtype=BF))
+                for _ in range(3)]
+        calls = [lambda w=w, b=b, o=o: lib.fluxb_modulation_gemv(vec.data_ptr(), w.data_ptr(), b.data_ptr(), o.data_ptr(), 1,
+                                                                  6 * Cc, Cc, 1, st) for w, b, o in bufs]
+        emit("modulation_projection[18432x3072]", time_calls(calls), 6 * Cc * Cc * 2, "hbm")
+    if want("linear_gelu"):
+        M, K, N = L, Cc, 4 * Cc
+        bufs = [(randn(M, K), randn(N, K, std=0.02), randn(N, std=0.02), torch.empty(M, N, device=dev, dtype=BF))
+                for _ in range(2)]
+        calls = [lambda x=x, w=w, b=b, y=y: linear_into(x, w, b, y, epi=_lib.EPI_GELU) for x, w, b, y in bufs]
+        emit("linear_bias_gelu[M4608,K3072,N12288]", time_calls(calls), 2.0 * M * N * K, "tensor")
+    if want("attention"):
+        bufs = [tuple(randn(1, Hh, L, D) for _ in range(3)) + (torch.empty(1, L, Hh, D, device=dev, dtype=BF),)
+                for _ in range(3)]
+        calls = [lambda q=q, k=k, v=v, o=o: attention_into(q, k, v, o.permute(0, 2, 1, 3), D ** -0.5) for q, k, v, o in bufs]
+        emit("attention[1,24,4608,128]", time_calls(calls), 4.0 * Hh * L * L * D, "tensor")
+    code, where = _lib.device_status()
+    if code != 0:
+        raise SystemExit(f"device status word reports error {code} at {where}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -190,7 +297,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | layer_norm_modulation | rms_norm | "
+                    "rope | qkv_prepare | modulation_projection | linear_gelu | attention")
     args = ap.parse_args()
+    if args.micro:
+        run_micro(args.micro, args.steps, args.warmup)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

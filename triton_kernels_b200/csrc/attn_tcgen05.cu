@@ -207,9 +207,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         for (int i = 0; i < 128; ++i)
           if (i >= valid) s[i] = 0xff800000u;  // -inf
       }
-      float mx = -INFINITY;
+      // eight independent running maxima keep the dependent chain 16 deep instead of 128
+      float mxs[8];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+      for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(s[i]);
+#pragma unroll
+      for (int i = 8; i < 128; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(s[i]));
+      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                             fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
       const float mx_scaled = mx * p.scale_log2;
 
       if (j == 0) {
@@ -233,7 +238,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       }
 
       const float neg_m = -m_used;
-      float sum0 = 0.f, sum1 = 0.f;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
@@ -241,13 +246,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         for (int i = 0; i < 16; ++i) {
           const float e0 = ex2(fmaf(__uint_as_float(s[c * 32 + 2 * i]), p.scale_log2, neg_m));
           const float e1 = ex2(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
-          sum0 += e0;
-          sum1 += e1;
+          sums[(i & 1) * 2] += e0;
+          sums[(i & 1) * 2 + 1] += e1;
           pk[i] = pack_bf16(e0, e1);
         }
         tmem_st_x16(s_addr + c * 16, pk);
       }
-      l += sum0 + sum1;
+      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[t]);

@@ -13,6 +13,7 @@
 // Tiles are handed out statically (tile = blockIdx.x + i * gridDim.x) in an order that keeps
 // 8 row-blocks of x and a band of w resident in L2 at a time.  Edge tiles rely on TMA zero
 // fill for loads and on masks for stores.  Every barrier wait is bounded.
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "common.cuh"
@@ -29,7 +30,6 @@ constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct Params {
@@ -43,17 +43,34 @@ struct Params {
   int split, epi, epi2, round_before_act;
   int tiles_m, tiles_n, num_tiles;
   int pair_stages;  // CTA-pair kernel: ring depth in use (<= gemm2::STAGES)
+  int raster_band_n, raster_group;  // tile order, see tile_coords
   DeviceStatus* status;
 };
 
-__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& m_blk, int& n_blk) {
-  const int per_group = GROUP_M * p.tiles_n;
-  const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int gsize = min(p.tiles_m - first_m, GROUP_M);
-  const int in_group = tile - group * per_group;
-  m_blk = first_m + in_group % gsize;
-  n_blk = in_group / gsize;
+// Tile order.  The tiles running at one time form a gm x gn rectangle of the output; all of
+// them walk K in step, so each x row-block and w row-block is fetched from HBM once per
+// rectangle and served from L2 to the others.  Across rectangles one operand is kept and the
+// other swept:
+//   band_n == 0: groups of `group` row-blocks of x are kept while all column-blocks are swept
+//   band_n == 1: bands of `group` column-blocks (rows of w) are kept while x is swept
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int tiles_m, int& m_blk, int& n_blk) {
+  if (p.raster_band_n == 0) {
+    const int per_group = p.raster_group * p.tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * p.raster_group;
+    const int gsize = min(tiles_m - first_m, p.raster_group);
+    const int in_group = tile - group * per_group;
+    m_blk = first_m + in_group % gsize;
+    n_blk = in_group / gsize;
+  } else {
+    const int per_band = p.raster_group * tiles_m;
+    const int band = tile / per_band;
+    const int first_n = band * p.raster_group;
+    const int bsize = min(p.tiles_n - first_n, p.raster_group);
+    const int in_band = tile - band * per_band;
+    n_blk = first_n + in_band % bsize;
+    m_blk = in_band / bsize;
+  }
 }
 
 // Applies the epilogue to 32 consecutive columns of one output row held in registers.
@@ -150,7 +167,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(p, tile, m_blk, n_blk);
+        tile_coords(p, tile, p.tiles_m, m_blk, n_blk);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           uint8_t* a_dst = smem + stage * STAGE_BYTES;
@@ -200,7 +217,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
       int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      tile_coords(p, tile, p.tiles_m, m_blk, n_blk);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
@@ -248,6 +265,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 namespace gemm2 {
 using gemm::Params;
 using gemm::epilogue_chunk;
+using gemm::tile_coords;
 constexpr int BM = 128;       // rows of x per CTA (256 per pair)
 constexpr int BN = 256;       // output columns per tile
 constexpr int BNH = 128;      // rows of w loaded by each CTA
@@ -258,18 +276,7 @@ constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int GROUP_M = 4;    // in 256-row blocks
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-
-__device__ __forceinline__ void tile_coords(const Params& p, int tile, int tiles_m, int& m_blk, int& n_blk) {
-  const int per_group = GROUP_M * p.tiles_n;
-  const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int gsize = min(tiles_m - first_m, GROUP_M);
-  const int in_group = tile - group * per_group;
-  m_blk = first_m + in_group % gsize;
-  n_blk = in_group / gsize;
-}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -486,6 +493,28 @@ extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void
   p.status = device_status_ptr();
   static const int stages_env = [] { const char* s = getenv("FLUXB_GEMM_PAIR_STAGES"); return (s && *s) ? atoi(s) : fluxb::gemm2::STAGES; }();
   p.pair_stages = stages_env < 2 ? 2 : (stages_env > fluxb::gemm2::STAGES ? fluxb::gemm2::STAGES : stages_env);
+  {
+    // Keep the smaller operand resident in L2 when it fits, sweep the larger one.
+    const int row_blk = use_pair ? 256 : 128;
+    const int tm = (int)((M + row_blk - 1) / row_blk);
+    const int tn = p.tiles_n;
+    const int concurrent = use_pair ? sm_count() / 2 : sm_count();
+    const double a_bytes = 2.0 * (double)M * (double)K, w_bytes = 2.0 * (double)N * (double)K;
+    const double keep_limit = 48e6;
+    if (a_bytes <= w_bytes) {
+      p.raster_band_n = 0;  // keep x row-blocks
+      p.raster_group = a_bytes <= keep_limit ? tm : (concurrent / tn > 1 ? concurrent / tn : 1);
+    } else {
+      p.raster_band_n = 1;  // keep w row-blocks
+      p.raster_group = w_bytes <= keep_limit ? tn : (concurrent / tm > 1 ? concurrent / tm : 1);
+    }
+    static const char* renv = getenv("FLUXB_GEMM_RASTER");  // "band_n,group" override for experiments
+    if (renv != nullptr && *renv != 0) {
+      int bn = 0, gr = 0;
+      if (sscanf(renv, "%d,%d", &bn, &gr) == 2 && gr > 0) { p.raster_band_n = bn; p.raster_group = gr; }
+    }
+    if (p.raster_group < 1) p.raster_group = 1;
+  }
 
   if (use_pair) {
     cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
