@@ -127,6 +127,31 @@ int fluxb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float
                        fluxb_stream_t stream);
 
 /*
+ * RMSNorm backward for callers that must not allocate.  (No counterpart in the reference: it
+ * allocates freely through torch.)
+ *
+ * Who needs it: code that runs where device allocation is off limits — inside a serving loop
+ * with a frozen memory plan, under a host-side allocator that forbids cudaMalloc after start-up,
+ * in a plugin whose host only hands it a stream and finished buffers.  fluxb_rms_norm_bwd asks
+ * such a caller for fp32 scratch; this entry point instead keeps the scratch in a fixed 4 MiB
+ * array inside the library image (resident on every GPU that loads the library, until exit)
+ * and also does the final reduction, so the caller passes only inputs and outputs:
+ *   dx [rows, cols] (dtype), dw [cols] fp32.
+ * It never calls cudaMalloc / cudaFree or any allocating routine.
+ * Limit: ceil(rows / 64) * cols <= fluxb_rms_norm_bwd_static_max_floats() (1 Mi floats);
+ * larger problems are rejected with FLUXB_ERR_UNSUPPORTED.
+ * The first call on each device looks the array's address up (a one-time host-side query);
+ * make that first call outside any stream capture.
+ * All calls on a device share the one array: two calls whose kernels may run at the same
+ * time (different streams, no ordering between them) race on it.  Calls ordered on one stream
+ * are safe, and no call depends on what an earlier one left in the array.
+ */
+int fluxb_rms_norm_bwd_static_max_floats(void);
+int fluxb_rms_norm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd,
+                              void* dx, float* dw, int64_t rows, int64_t cols, int dtype,
+                              fluxb_stream_t stream);
+
+/*
  * Rotary embedding with a general 2x2 table: out[2i+j] = pe[l,i,j,0]*x[2i] + pe[l,i,j,1]*x[2i+1]
  * for q and k.  Replaces triton_kernels/kernels/positional_embedding.py:55-82 (`apply_rope`,
  * kernel `_rope_fwd` :9-52).  q,k,oq,ok: contiguous [BH, L, D]; pe: fp32 [L, D/2, 2, 2].

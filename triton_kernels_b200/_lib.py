@@ -31,6 +31,8 @@ SIGNATURES = {
     "fluxb_rms_norm": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P]),
     "fluxb_rms_norm_bwd_partial_rows": (_I, [_L]),
     "fluxb_rms_norm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P]),
+    "fluxb_rms_norm_bwd_static_max_floats": (_I, []),
+    "fluxb_rms_norm_bwd_static": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P]),
     "fluxb_rope": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P]),
     "fluxb_qkv_prep": (_I, [_P, _L, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _F, _P]),
     "fluxb_modulation_scale_shift": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _I, _P]),

@@ -10,6 +10,8 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fluxb {
@@ -372,6 +374,28 @@ rms_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __res
     for (int wi = 0; wi < 8; ++wi) s += dw_smem[(int64_t)wi * cols + c];
     dw_partial[(int64_t)blockIdx.x * cols + c] = s;
   }
+}
+
+// ----------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation: the per-block partial sums of dw go to a fixed
+// array that is part of the library image instead of caller-provided scratch.
+//
+// The array lives in device global memory of every GPU that loads the library, from load
+// until the process exits (4 MiB per GPU).  Its name is only a handle in host code — it is
+// not a device address there — so the host resolves the real address once per device with
+// cudaGetSymbolAddress (see static_dw_scratch below) and passes that pointer to the kernels.
+// ----------------------------------------------------------------------------------------
+constexpr int64_t kStaticDwScratchFloats = 1 << 20;  // 1 Mi floats = 4 MiB
+static __device__ __align__(256) float g_static_dw_scratch[kStaticDwScratchFloats];
+
+// dw[c] = sum over the `parts` partial rows; one thread per column, fixed order (deterministic).
+__global__ void __launch_bounds__(256)
+reduce_dw_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw, int parts, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int r = 0; r < parts; ++r) s += partial[(int64_t)r * cols + c];
+  dw[c] = s;
 }
 
 // ----------------------------------------------------------------------------------------
@@ -751,6 +775,63 @@ extern "C" int fluxb_rms_norm_bwd(const void* dy, const void* x, const void* w, 
                                   rows, (int)cols);
   }
   return launch_status("rms_norm_bwd");
+}
+
+// Address of g_static_dw_scratch on the current device, resolved on first use per device.
+static float* static_dw_scratch(int* err) {
+  static std::mutex mu;
+  static float* ptrs[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = set_error(FLUXB_ERR_CUDA, "rms_norm_bwd_static: cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_dw_scratch);  // needs `dev` current, which it is
+    if (e != cudaSuccess || p == nullptr) {
+      *err = set_error(FLUXB_ERR_CUDA, "rms_norm_bwd_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  return ptrs[dev];
+}
+
+extern "C" int fluxb_rms_norm_bwd_static_max_floats(void) { return (int)kStaticDwScratchFloats; }
+
+extern "C" int fluxb_rms_norm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd,
+                                         void* dx, float* dw, int64_t rows, int64_t cols, int dtype,
+                                         fluxb_stream_t stream) {
+  if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "rms_norm_bwd_static: dtype %d", dtype);
+  if (rows < 0 || cols <= 0) return set_error(FLUXB_ERR_BAD_ARG, "rms_norm_bwd_static: bad sizes");
+  if (!dw) return set_error(FLUXB_ERR_BAD_ARG, "rms_norm_bwd_static: null dw");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    cudaError_t e = cudaMemsetAsync(dw, 0, (size_t)cols * sizeof(float), st);
+    if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "rms_norm_bwd_static: %s", cudaGetErrorString(e));
+    return FLUXB_OK;
+  }
+  const int64_t parts = fluxb_rms_norm_bwd_partial_rows(rows);
+  if (parts * cols > kStaticDwScratchFloats)
+    return set_error(FLUXB_ERR_UNSUPPORTED,
+                     "rms_norm_bwd_static: ceil(rows/%d) * cols = %lld floats of scratch needed, the built-in array "
+                     "holds %lld; use fluxb_rms_norm_bwd with caller scratch",
+                     kRmsBwdRowsPerBlock, (long long)(parts * cols), (long long)kStaticDwScratchFloats);
+  int err = FLUXB_OK;
+  float* scratch = static_dw_scratch(&err);
+  if (scratch == nullptr) return err;
+  // Stage 1: the ordinary backward kernel, writing its partial rows into the built-in array.
+  // Every element of the region that stage 2 reads is overwritten here, so nothing left by an
+  // earlier call can leak into this one and nothing needs clearing first.
+  int rc = fluxb_rms_norm_bwd(dy, x, w, rstd, dx, scratch, rows, cols, dtype, stream);
+  if (rc != FLUXB_OK) return rc;
+  // Stage 2: fold the partial rows into the caller's dw.
+  reduce_dw_partials_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, st>>>(scratch, dw, (int)parts, (int)cols);
+  return launch_status("rms_norm_bwd_static");
 }
 
 extern "C" int fluxb_rope(const void* q, const void* k, const float* pe, void* oq, void* ok,
