@@ -29,6 +29,7 @@ constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_SLOTS * TILE_BYTES + 1024 + 256;
 constexpr float kRescaleThreshold = 8.0f;
+// kPolyEvery (kernel template parameter): every n-th pair of a row takes the polynomial exp2; 1000 = none.
 
 struct Params {
   __nv_bfloat16* o;
@@ -45,6 +46,69 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// exp2 of two values on the FMA pipes (no MUFU): round to the nearest integer n with the
+// magic-number trick, evaluate a cubic for 2^f on f = x - n in [-0.5, 0.5] (max relative error
+// 7.7e-5, far below the bf16 rounding of P), then add n into the exponent field.  Inputs are
+// clamped at -126 so the exponent cannot wrap.  A share of every row goes this way so that the
+// 16-lane-per-clock MUFU is not the only engine producing exponentials.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  const float kMagic = 12582912.0f;  // 1.5 * 2^23
+  x.x = fmaxf(x.x, -126.0f);
+  x.y = fmaxf(x.y, -126.0f);
+  const float2 t = __fadd2_rn(x, make_float2(kMagic, kMagic));
+  const float2 r = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+  const float2 f = __fadd2_rn(x, make_float2(-r.x, -r.y));
+  float2 p = __ffma2_rn(f, make_float2(0.05508877709507942f, 0.05508877709507942f),
+                        make_float2(0.242604061961174f, 0.242604061961174f));
+  p = __ffma2_rn(p, f, make_float2(0.6932762265205383f, 0.6932762265205383f));
+  p = __ffma2_rn(p, f, make_float2(0.9999289512634277f, 0.9999289512634277f));
+  float2 out;
+  out.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
+  out.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
+  return out;
+}
+
+// MMA issue with the accumulate flag known at compile time and descriptors given as
+// (low word, high word): only the low word changes from one K step to the next.
+template <int kAccumulate>
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                       uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAccumulate)
+      : "memory");
+}
+template <int kAccumulate>
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                       uint32_t idesc) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAccumulate)
+      : "memory");
+}
+
+template <int kPolyEvery>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -124,25 +188,35 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const uint32_t kv_addr = smem_u32(kv_smem);
       bool ok = true;
 
+      // Descriptor words.  High word: stride offset, descriptor version, 128-byte swizzle.
+      const uint32_t hi_kmajor = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t hi_v = (p.v_sbo >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t v_lbo_field = ((p.v_lbo >> 4) & 0x3fffu) << 16;
+      const uint32_t q_lo = (q_addr & 0x3ffffu) >> 4;
+      const uint32_t kv_lo = (kv_addr & 0x3ffffu) >> 4;
+
       auto issue_qk = [&](int t, int slot) {
-        const uint32_t qa = q_addr + t * TILE_BYTES;
-        const uint32_t ka = kv_addr + slot * TILE_BYTES;
+        const uint32_t qa = q_lo + t * (TILE_BYTES >> 4);
+        const uint32_t ka = kv_lo + slot * (TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + t * 128;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_ss(tmem_base + t * 128, make_smem_desc(qa + off, 16, 1024),
-                  make_smem_desc(ka + off, 16, 1024), idesc_qk, ks != 0 ? 1u : 0u);
+          // 16 elements of head_dim per step: 32 bytes inside a 128-byte row, second half-block
+          // after four steps
+          const uint32_t off = (ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2;
+          if (ks == 0) mma_ss<0>(d, qa + off, hi_kmajor, ka + off, hi_kmajor, idesc_qk);
+          else mma_ss<1>(d, qa + off, hi_kmajor, ka + off, hi_kmajor, idesc_qk);
         }
       };
       auto issue_pv = [&](int t, int slot, bool accumulate) {
-        const uint32_t va = kv_addr + slot * TILE_BYTES;
+        const uint32_t va = (kv_lo + slot * (TILE_BYTES >> 4)) | v_lbo_field;
+        const uint32_t d = tmem_base + 256 + t * 128;
+        const uint32_t pa = tmem_base + t * 128;
+        // 16 keys per step: 16 rows of 128 bytes in each half-block; 8 TMEM columns of P.
+        if (accumulate) mma_ts<1>(d, pa, va, hi_v, idesc_pv);
+        else mma_ts<0>(d, pa, va, hi_v, idesc_pv);
 #pragma unroll
-        for (int ks = 0; ks < BKV / 16; ++ks) {
-          // 16 keys per step: 16 rows of 128 bytes in each half-block; 8 TMEM columns of P.
-          umma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + ks * 8,
-                  make_smem_desc(va + ks * 16 * 128, p.v_lbo, p.v_sbo), idesc_pv,
-                  (accumulate || ks != 0) ? 1u : 0u);
-        }
+        for (int ks = 1; ks < BKV / 16; ++ks) mma_ts<1>(d, pa + ks * 8, va + ks * 128, hi_v, idesc_pv);
       };
 
       ok = mbar_wait(q_full, 0, abort_flag, p.status, 21);
@@ -207,14 +281,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         for (int i = 0; i < 128; ++i)
           if (i >= valid) s[i] = 0xff800000u;  // -inf
       }
-      // eight independent running maxima keep the dependent chain 16 deep instead of 128
-      float mxs[8];
+      // four independent running maxima, two new elements per 3-input max
+      float mxs[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mxs[i] = __uint_as_float(s[i]);
+      for (int i = 0; i < 4; ++i) mxs[i] = __uint_as_float(s[i]);
 #pragma unroll
-      for (int i = 8; i < 128; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(s[i]));
-      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
-                             fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+      for (int i = 4; i < 128; i += 2)
+        mxs[(i >> 1) & 3] = max3(mxs[(i >> 1) & 3], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+      const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       const float mx_scaled = mx * p.scale_log2;
 
       if (j == 0) {
@@ -237,22 +311,29 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
       }
 
-      const float neg_m = -m_used;
-      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+      const float2 neg_m2 = make_float2(-m_used, -m_used);
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      float2 sums[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float e0 = ex2(fmaf(__uint_as_float(s[c * 32 + 2 * i]), p.scale_log2, neg_m));
-          const float e1 = ex2(fmaf(__uint_as_float(s[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
-          sums[(i & 1) * 2] += e0;
-          sums[(i & 1) * 2 + 1] += e1;
-          pk[i] = pack_bf16(e0, e1);
+          const float2 x = __ffma2_rn(
+              make_float2(__uint_as_float(s[c * 32 + 2 * i]), __uint_as_float(s[c * 32 + 2 * i + 1])), scale2, neg_m2);
+          float2 e;
+          if ((i % kPolyEvery) == kPolyEvery - 1) {
+            e = exp2_poly2(x);
+          } else {
+            e.x = ex2(x.x);
+            e.y = ex2(x.y);
+          }
+          sums[i & 1] = __fadd2_rn(sums[i & 1], e);
+          pk[i] = pack_bf16(e.x, e.y);
         }
         tmem_st_x16(s_addr + c * 16, pk);
       }
-      l += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      l += (sums[0].x + sums[0].y) + (sums[1].x + sums[1].y);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[t]);
@@ -351,10 +432,16 @@ extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void
   p.v_sbo = env_u32("FLUXB_ATTN_V_SBO", 1024);
   p.status = device_status_ptr();
 
-  cudaError_t e = cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  static const int poly_env = (int)env_u32("FLUXB_ATTN_POLY", 4);
+  auto kern = attn_kernel<4>;
+  if (poly_env == 0) kern = attn_kernel<1000>;
+  else if (poly_env == 2) kern = attn_kernel<2>;
+  else if (poly_env == 3) kern = attn_kernel<3>;
+  else if (poly_env == 8) kern = attn_kernel<8>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: cannot set shared memory size: %s", cudaGetErrorString(e));
   dim3 grid((unsigned)((Lq + 2 * BQ - 1) / (2 * BQ)), (unsigned)H, (unsigned)B);
-  attn_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, p);
+  kern<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
