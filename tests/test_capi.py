@@ -92,3 +92,26 @@ def test_state_dict_keys_match_reference_layout():
     assert {k: tuple(v.shape) for k, v in d.state_dict().items()} == cases.double_block_shapes(256, 1024)
     s.load_state_dict(cases.case_single_block_small()["params"])
     d.load_state_dict(cases.case_double_block_small()["params"])
+
+
+def test_package_embedders_match_reference_golden(golden):
+    """The PyTorch-side pieces of the DiT assembly (RoPE table, timestep embedding) against the
+    reference's own outputs; they run on any device."""
+    import cases
+
+    from triton_kernels_b200.flux import EmbedND, flux_position_ids, timestep_embedding
+
+    c = cases.case_embed_nd()
+    pe = EmbedND(128, c["theta"], c["axes_dim"])(c["ids"])
+    torch.testing.assert_close(pe, golden["embed_nd"]["pe"], atol=1e-6, rtol=0)
+    torch.testing.assert_close(flux_position_ids(8, 4, 6), c["ids"], atol=0, rtol=0)
+    t = cases.case_timestep_embedding()
+    torch.testing.assert_close(timestep_embedding(t["t"], t["dim"]), golden["timestep_embedding"]["emb"], atol=1e-6, rtol=0)
+
+
+def test_dit_state_dict_keys_match_oracle_layout():
+    from oracle import flux_oracle as O
+    from triton_kernels_b200.flux import FluxDiT, FluxParams
+
+    m = FluxDiT(FluxParams(hidden_size=256, num_heads=2, depth=1, depth_single_blocks=2, context_in_dim=96))
+    assert {k: tuple(v.shape) for k, v in m.state_dict().items()} == O.dit_shapes(256, 64, 96, 1, 2)

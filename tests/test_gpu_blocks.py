@@ -119,3 +119,49 @@ def test_unfused_module_pieces_match_fused_block(tk):
     chunks = O.modulation(vec.float(), msd, "", double=True)
     torch.testing.assert_close(m2.gate.float().cpu(), chunks[5], atol=2e-2, rtol=2e-2)
     assert m1.shift.shape == (2, 1, C)
+
+
+def _small_dit(tk, C, H, depth, depth_single, ctx, seed):
+    from triton_kernels_b200.flux import FluxDiT, FluxParams
+
+    g = torch.Generator().manual_seed(seed)
+    params = O.init_params(O.dit_shapes(C, 64, ctx, depth, depth_single), g, bias_std=0.02, scale_jitter=0.1)
+    pb = bf16_params(params)
+    model = FluxDiT(FluxParams(hidden_size=C, num_heads=H, depth=depth, depth_single_blocks=depth_single,
+                               context_in_dim=ctx)).to(BF)
+    model.load_state_dict(pb)
+    return model.cuda(), {k: v.float() for k, v in pb.items()}, g
+
+
+@pytest.mark.parametrize("C,H,gh,gw,Lt", [(256, 2, 6, 8, 16), (3072, 24, 16, 16, 64)])
+def test_dit_forward_against_oracle(tk, C, H, gh, gw, Lt):
+    """Whole-model wiring (in/out layers, embedders, 2 double + 3 single blocks) at reduced
+    depth; hidden 3072 keeps the real block shapes."""
+    ctx = 128
+    model, pf, g = _small_dit(tk, C, H, 2, 3, ctx, seed=31)
+    img = torch.randn(1, gh * gw, 64, generator=g).to(BF)
+    txt = torch.randn(1, Lt, ctx, generator=g).to(BF)
+    t, gd = torch.tensor([0.5]), torch.tensor([3.5])
+    pe = O.embed_nd(O.flux_position_ids(Lt, gh, gw), [16, 56, 56])
+    y = model(img.cuda(), txt.cuda(), t.cuda(), gd.cuda(), pe.cuda())
+    want = O.flux_dit_forward(img.float(), txt.float(), t, gd, pe, pf, H, 2, 3)
+    assert y.shape == (1, gh * gw, 64)
+    assert rel_l2(y, want) < 2e-2  # five blocks deep: twice the single-block bound
+
+
+def test_dit_graph_replay_matches_eager(tk):
+    from triton_kernels_b200.flux import GraphedForward
+
+    C, H, gh, gw, Lt, ctx = 256, 2, 8, 8, 32, 128
+    model, _, g = _small_dit(tk, C, H, 1, 2, ctx, seed=32)
+    pe = O.embed_nd(O.flux_position_ids(Lt, gh, gw), [16, 56, 56]).cuda()
+    mk = lambda: (torch.randn(1, gh * gw, 64, generator=g).to(BF).cuda(), torch.randn(1, Lt, ctx, generator=g).to(BF).cuda(),
+                  torch.tensor([0.25]).cuda(), torch.tensor([3.5]).cuda())
+    a, b = mk(), mk()
+    with torch.no_grad():
+        graphed = GraphedForward(lambda i, x, t, gd: model(i, x, t, gd, pe), a)
+        for inp in (a, b, a):
+            want = model(*inp, pe)
+            got = graphed(*inp)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)  # same kernels, same inputs: bit-identical
