@@ -290,6 +290,68 @@ def run_micro(which: str, steps: int, warmup: int):
         raise SystemExit(f"device status word reports error {code} at {where}")
 
 
+# --------------------------------------------------------------------------------------
+# Full Flux DiT denoising step (19 double + 38 single blocks, 4096 + 512 tokens, batch 1,
+# weights N(0,0.02) drawn on the device with seed 3): one JSON line with the step latency,
+# eager and as a CUDA-graph replay.
+# --------------------------------------------------------------------------------------
+def run_dit(steps: int, warmup: int, depth: int = 19, depth_single: int = 38):
+    from triton_kernels_b200 import _lib
+    from triton_kernels_b200.flux import EmbedND, FluxDiT, FluxParams, GraphedForward, flux_position_ids
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    BF = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(3)
+    with torch.device(dev):
+        model = FluxDiT(FluxParams(depth=depth, depth_single_blocks=depth_single)).to(BF)
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if name.endswith(".scale"):
+                prm.fill_(1.0)
+            elif name.endswith(".bias"):
+                prm.zero_()
+            else:
+                prm.copy_((torch.randn(prm.shape, device=dev, generator=g) * 0.02).to(BF))
+    img = torch.randn(1, L_IMG, 64, device=dev, generator=g).to(BF)
+    txt = torch.randn(1, L_TXT, 4096, device=dev, generator=g).to(BF)
+    t = torch.tensor([0.5], device=dev)
+    gd = torch.tensor([3.5], device=dev)
+    pe = EmbedND(128, 10000, [16, 56, 56])(flux_position_ids(L_TXT, GRID, GRID, device=dev))
+    fwd = lambda i, x, tt, gg: model(i, x, tt, gg, pe)
+
+    def timed(fn):
+        for _ in range(max(warmup, 1)):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(max(steps, 1)):
+            out = fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / max(steps, 1), out
+
+    with torch.no_grad():
+        calls0 = _lib.kernel_calls
+        fwd(img, txt, t, gd)
+        launches = _lib.kernel_calls - calls0
+        eager_ms, out = timed(lambda: fwd(img, txt, t, gd))
+        graphed = GraphedForward(fwd, (img, txt, t, gd))
+        graph_ms, out_g = timed(lambda: graphed(img, txt, t, gd))
+    finite = bool(torch.isfinite(out.float()).all()) and bool(torch.equal(out, out_g))
+    code, where = _lib.device_status()
+    n_blocks = depth + depth_single
+    flop = n_blocks * BLOCK_FLOP + 2 * L_IMG * 64 * C * 2 + 2 * L_TXT * 4096 * C
+    print(json.dumps({
+        "workload": f"flux_dit_step {depth} double + {depth_single} single blocks, {L_IMG}+{L_TXT} tokens, batch 1, bf16",
+        "ms_per_step_eager": eager_ms, "ms_per_step_graph": graph_ms, "tokens_per_s_graph": TOKENS / (graph_ms * 1e-3),
+        "tflop_per_step": flop / 1e12, "tflops_achieved_graph": flop / (graph_ms * 1e-3) / 1e12,
+        "kernel_calls_per_step": launches, "output_finite_and_graph_equals_eager": finite, "device_status": [code, where],
+        "params_gb": sum(p.numel() for p in model.parameters()) * 2 / 1e9,
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -297,11 +359,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")
     ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | layer_norm_modulation | rms_norm | "
                     "rope | qkv_prepare | modulation_projection | linear_gelu | attention")
     args = ap.parse_args()
     if args.micro:
         run_micro(args.micro, args.steps, args.warmup)
+        return
+    if args.dit:
+        run_dit(args.steps, args.warmup)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
