@@ -352,6 +352,90 @@ def run_dit(steps: int, warmup: int, depth: int = 19, depth_single: int = 38):
     }), flush=True)
 
 
+# --------------------------------------------------------------------------------------
+# Ulysses sequence parallelism (benchmark config 5b): ONE double-stream block over a
+# 128x128-patch image (16384 image + 512 text tokens, batch 1) with the tokens sharded over the
+# ranks and an all-to-all on heads around attention.  Strong scaling: the total work is fixed.
+# --------------------------------------------------------------------------------------
+def run_ulysses(args, rank: int, local_rank: int, world: int):
+    import torch.distributed as dist
+
+    import triton_kernels_b200 as tk
+    from triton_kernels_b200 import _lib
+    from triton_kernels_b200.flux import EmbedND, flux_position_ids
+    from triton_kernels_b200.parallel import SequenceParallel, shard_joint_sequence
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    BF = torch.bfloat16
+    li, lt, grid = 16384, 512, 128
+    g = torch.Generator(device=dev).manual_seed(4)  # same parameters and inputs on every rank
+    with torch.device(dev):
+        block = tk.DoubleStreamBlock(C, H, MLP_RATIO).to(BF)
+    with torch.no_grad():
+        for name, prm in block.named_parameters():
+            if name.endswith(".scale"):
+                prm.fill_(1.0)
+            elif name.endswith(".bias"):
+                prm.zero_()
+            else:
+                prm.copy_((torch.randn(prm.shape, device=dev, generator=g) * 0.02).to(BF))
+    img = torch.randn(1, li, C, device=dev, generator=g).to(BF)
+    txt = torch.randn(1, lt, C, device=dev, generator=g).to(BF)
+    vec = torch.randn(1, C, device=dev, generator=g).to(BF)
+    pe = EmbedND(128, 10000, [16, 56, 56])(flux_position_ids(lt, grid, grid, device=dev))
+    if world > 1:
+        block.sequence_parallel = SequenceParallel()
+        txt, img, pe = shard_joint_sequence(txt, img, pe, rank, world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            block(img, txt, vec, pe)
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        barrier()
+        calls0 = _lib.kernel_calls
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            block(img, txt, vec, pe)
+        e1.record()
+        barrier()
+        launches = _lib.kernel_calls - calls0
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    code, where = _lib.device_status()
+    if code != 0:
+        raise SystemExit(f"device status word reports error {code} at {where}")
+    if rank == 0:
+        tokens = li + lt
+        flop = 2 * tokens * C * (3 * C + C + 2 * int(C * MLP_RATIO)) + 4 * H * tokens * tokens * (C // H)
+        print(json.dumps({
+            "metric": "flux_double_block_fwd_tokens_per_s", "value": tokens * args.steps / (ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"flux_double_stream_block hidden {C}, {H} heads x 128, {li} image + {lt} text tokens, "
+                                   "batch 1 in total, weights N(0,0.02), seed 4",
+                       "parallelism": f"ulysses sequence-parallel x{world} (all-to-all on heads, NCCL)",
+                       "block_tflop": flop / 1e12, "tflops_per_gpu": flop * args.steps / (ms * 1e-3) / 1e12 / world},
+            "gpu_launches": launches, "clocks": clocks,
+        }), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -359,6 +443,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="dp", choices=["dp", "ulysses"],
+                    help="multi-GPU sharding: batch data-parallel (default, weak scaling) or Ulysses sequence parallelism "
+                         "on a 16384+512-token block (strong scaling)")
     ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")
     ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | layer_norm_modulation | rms_norm | "
                     "rope | qkv_prepare | modulation_projection | linear_gelu | attention")
@@ -377,6 +464,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.parallel == "ulysses":
+        run_ulysses(args, rank, local_rank, world)
         return
 
     import torch.distributed as dist

@@ -169,11 +169,17 @@ int fluxb_rope(const void* q, const void* k, const float* pe, void* oq, void* ok
  * (QKNorm at triton_kernels/modules/normalization.py:19-26).
  *   src_s: [B, L_s, ld_s] with the q|k|v columns first; qscale_s/kscale_s: [D] bf16 or NULL.
  *   pe: fp32 [L, D/2, 2, 2] or NULL.  D must be 128.  bf16 only.
+ *   Output addressing: heads_per_group <= 0 means contiguous [B,H,L,D].  Otherwise element
+ *   (b, h, l, :) of q, k and v lands at b*o_sb + (h / heads_per_group)*o_sg +
+ *   (h % heads_per_group)*o_sh + l*o_sl, which lets a sequence-parallel caller have the rows
+ *   written directly in the per-destination-rank layout of its head all-to-all (no counterpart
+ *   in the reference, which has no multi-GPU path).
  */
 int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
                    const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
                    const void* qscale1, const void* kscale1, const float* pe, void* q, void* k,
-                   void* v, int64_t B, int64_t H, int64_t D, float eps, fluxb_stream_t stream);
+                   void* v, int64_t B, int64_t H, int64_t D, int64_t heads_per_group, int64_t o_sb,
+                   int64_t o_sg, int64_t o_sh, int64_t o_sl, float eps, fluxb_stream_t stream);
 
 /*
  * out = (1 + scale) * x + shift with shift/scale taken from the packed modulation tensor

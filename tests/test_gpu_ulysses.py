@@ -1,0 +1,90 @@
+"""Ulysses sequence parallelism on real GPUs (needs at least two): each rank's shard of the
+sequence-parallel block output equals the corresponding rows of the single-GPU block output.
+Ranks are child processes over NCCL with NVLS switched off; a rank only leaves between steps."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank: int, world: int, port: int, q_out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from oracle import flux_oracle as O
+        import triton_kernels_b200 as tk
+        from triton_kernels_b200.parallel import SequenceParallel, shard_joint_sequence
+
+        BF = torch.bfloat16
+        C, H, Lt, gh, gw = 3072, 24, 64, 16, 16
+        g = torch.Generator().manual_seed(41)  # same draw on every rank
+        pd = {k: v.to(BF) for k, v in O.init_params(O.double_block_shapes(C), g, bias_std=0.02, scale_jitter=0.1).items()}
+        ps = {k: v.to(BF) for k, v in O.init_params(O.single_block_shapes(C), g, bias_std=0.02, scale_jitter=0.1).items()}
+        img = torch.randn(1, gh * gw, C, generator=g).to(BF).cuda()
+        txt = torch.randn(1, Lt, C, generator=g).to(BF).cuda()
+        vec = torch.randn(1, C, generator=g).to(BF).cuda()
+        pe = O.embed_nd(O.flux_position_ids(Lt, gh, gw), [16, 56, 56]).cuda()
+        dblk = tk.DoubleStreamBlock(C, H, 4.0).to(BF)
+        dblk.load_state_dict(pd)
+        dblk = dblk.cuda()
+        sblk = tk.SingleStreamBlock(C, H, 4.0).to(BF)
+        sblk.load_state_dict(ps)
+        sblk = sblk.cuda()
+
+        with torch.no_grad():
+            want_img, want_txt = dblk(img, txt, vec, pe)
+            want_x = sblk(torch.cat((txt, img), 1), vec, pe)
+            sp = SequenceParallel()
+            dblk.sequence_parallel = sblk.sequence_parallel = sp
+            txt_l, img_l, pe_l = shard_joint_sequence(txt, img, pe, rank, world)
+            got_img, got_txt = dblk(img_l, txt_l, vec, pe_l)
+            got_x = sblk(torch.cat((txt_l, img_l), 1), vec, pe_l)
+        torch.cuda.synchronize()
+        Li, Ltl = img.shape[1] // world, Lt // world
+        rows_i = slice(rank * Li, (rank + 1) * Li)
+        rows_t = slice(rank * Ltl, (rank + 1) * Ltl)
+
+        def rel(a, b):
+            return float((a.float() - b.float()).norm() / b.float().norm())
+
+        # same kernels and weights; only the key order inside attention differs
+        errs = [rel(got_img, want_img[:, rows_i]), rel(got_txt, want_txt[:, rows_t]),
+                rel(got_x[:, :Ltl], want_x[:, rows_t]), rel(got_x[:, Ltl:], want_x[:, Lt:][:, rows_i])]
+        dist.barrier()
+        q_out.put((rank, max(errs)))
+    except Exception as e:  # noqa: BLE001
+        q_out.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_parallel_blocks_match_single_gpu(lib):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    world = 2
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q_out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q_out.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err in results:
+        assert isinstance(err, float), f"rank {rank}: {err}"
+        assert err < 5e-3, f"rank {rank}: sequence-parallel output differs from single-GPU output by {err}"

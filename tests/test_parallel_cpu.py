@@ -1,0 +1,94 @@
+"""Host-side logic of the multi-GPU shardings on CPU ranks (gloo, world size 2): the Ulysses
+all-to-all layouts reproduce full attention, and the batch / token shard helpers partition
+their inputs exactly."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import flux_oracle as O
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _ulysses_rank(rank: int, world: int, port: int, B: int, q_out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from triton_kernels_b200.parallel import SequenceParallel
+
+        sp = SequenceParallel()
+        H, D, L = 4, 16, 24
+        g = torch.Generator().manual_seed(77)
+        q, k, v = (torch.randn(B, H, L, D, generator=g) for _ in range(3))
+        want = O.scaled_dot_product_attention(q, k, v).permute(0, 2, 1, 3).reshape(B, L, H * D)
+        L_loc = L // world
+        rows = slice(rank * L_loc, (rank + 1) * L_loc)
+        # what the q/k/v assembly kernel writes for this rank's tokens
+        shape, (Hp, sb, sg, sh, sl) = sp.send_layout(B, L_loc, H, D)
+        send = torch.zeros(shape)
+        flat = send.view(-1)
+        for i, t in enumerate((q, k, v)):
+            for b in range(B):
+                for h in range(H):
+                    for l in range(L_loc):
+                        off = i * Hp * D + b * sb + (h // Hp) * sg + (h % Hp) * sh + l * sl
+                        flat[off : off + D] = t[b, h, rows][l]
+        full = sp.tokens_to_heads(send)  # [B, L, 3, Hp, D]
+        assert full.shape == (B, L, 3, Hp, D)
+        qh, kh, vh = (full[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        torch.testing.assert_close(qh, q[:, rank * Hp : (rank + 1) * Hp])  # all tokens, local heads, original order
+        o = O.scaled_dot_product_attention(qh, kh, vh).permute(0, 2, 1, 3).reshape(B, L, Hp * D).contiguous()
+        wide = torch.zeros(B, L_loc, H * D + 8)
+        got = sp.heads_to_tokens(o, wide[:, :, : H * D])
+        torch.testing.assert_close(got, want[:, rows], atol=1e-6, rtol=1e-6)
+        assert float(wide[:, :, H * D :].abs().max()) == 0.0
+        q_out.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q_out.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_ulysses_exchange_reproduces_full_attention(B):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ulysses_rank, args=(r, world, port, B, q_out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q_out.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_shard_helpers_partition_exactly():
+    from triton_kernels_b200.parallel import shard_batch, shard_joint_sequence
+
+    for batch, world in [(8, 8), (8, 4), (5, 2), (3, 4)]:
+        got = [i for r in range(world) for i in range(batch)[shard_batch(batch, r, world)]]
+        assert got == list(range(batch))
+    Lt, Li = 8, 24
+    txt = torch.arange(Lt).float().view(1, Lt, 1)
+    img = 100 + torch.arange(Li).float().view(1, Li, 1)
+    pe = torch.arange(Lt + Li).float().view(1, 1, Lt + Li, 1, 1, 1).expand(1, 1, Lt + Li, 2, 2, 2)
+    seen_t, seen_i = [], []
+    for r in range(4):
+        t, i, p = shard_joint_sequence(txt, img, pe, r, 4)
+        seen_t += t.flatten().tolist()
+        seen_i += i.flatten().tolist()
+        # table rows follow the local order: this rank's text rows, then its image rows
+        assert p[0, 0, :, 0, 0, 0].tolist() == t.flatten().tolist() + [x - 100 + Lt for x in i.flatten().tolist()]
+    assert seen_t == txt.flatten().tolist() and seen_i == img.flatten().tolist()
+    with pytest.raises(AssertionError):
+        shard_joint_sequence(txt, img, pe, 0, 3)

@@ -34,7 +34,7 @@ SIGNATURES = {
     "fluxb_rms_norm_bwd_static_max_floats": (_I, []),
     "fluxb_rms_norm_bwd_static": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P]),
     "fluxb_rope": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P]),
-    "fluxb_qkv_prep": (_I, [_P, _L, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _F, _P]),
+    "fluxb_qkv_prep": (_I, [_P, _L, _L, _P, _P, _P, _L, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _F, _P]),
     "fluxb_modulation_scale_shift": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _I, _P]),
     "fluxb_modulation_gate_proj": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _P]),
     "fluxb_silu": (_I, [_P, _P, _L, _I, _P]),

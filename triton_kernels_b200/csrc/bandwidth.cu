@@ -492,6 +492,8 @@ struct QkvPrepArgs {
   __nv_bfloat16* k;
   __nv_bfloat16* v;
   int64_t B, H, L;
+  // output addressing: element offset = b*o_sb + (h / hpg)*o_sg + (h % hpg)*o_sh + l*o_sl
+  int64_t o_sb, o_sg, o_sh, o_sl, hpg;
   float eps;
 };
 
@@ -538,7 +540,7 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
   for (int hh = 0; hh < HG; ++hh) {
     const int64_t h = h0 + hh;
     if (h >= a.H) continue;  // uniform across the block (depends on blockIdx.y only)
-    const int64_t out_off = ((b * a.H + h) * a.L + l) * D + lane16 * 8;
+    const int64_t out_off = b * a.o_sb + (h / a.hpg) * a.o_sg + (h % a.hpg) * a.o_sh + l * a.o_sl + lane16 * 8;
 #pragma unroll
     for (int part = 0; part < 2; ++part) {
       Vec<__nv_bfloat16> xv;
@@ -863,7 +865,8 @@ extern "C" int fluxb_rope(const void* q, const void* k, const float* pe, void* o
 extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
                               const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
                               const void* qscale1, const void* kscale1, const float* pe, void* q,
-                              void* k, void* v, int64_t B, int64_t H, int64_t D, float eps,
+                              void* k, void* v, int64_t B, int64_t H, int64_t D, int64_t heads_per_group,
+                              int64_t o_sb, int64_t o_sg, int64_t o_sh, int64_t o_sl, float eps,
                               fluxb_stream_t stream) {
   if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "qkv_prep: head_dim %lld (only 128)", (long long)D);
   if (B < 0 || H <= 0 || L0 < 0 || L1 < 0) return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: bad sizes");
@@ -897,6 +900,13 @@ extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const v
   a.k = static_cast<__nv_bfloat16*>(k);
   a.v = static_cast<__nv_bfloat16*>(v);
   a.B = B; a.H = H; a.L = L; a.eps = eps;
+  if (heads_per_group <= 0) {  // default: contiguous [B, H, L, D]
+    a.hpg = H; a.o_sg = 0; a.o_sb = H * L * D; a.o_sh = L * D; a.o_sl = D;
+  } else {
+    if (H % heads_per_group || o_sb % 8 || o_sg % 8 || o_sh % 8 || o_sl % 8 || o_sl < D)
+      return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: heads_per_group must divide H and output strides must be multiples of 8 (row stride >= D)");
+    a.hpg = heads_per_group; a.o_sg = o_sg; a.o_sb = o_sb; a.o_sh = o_sh; a.o_sl = o_sl;
+  }
   constexpr int HG = 4;
   dim3 grid((unsigned)((B * L + 15) / 16), (unsigned)((H + HG - 1) / HG));
   qkv_prep_kernel<HG><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);

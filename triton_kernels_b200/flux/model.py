@@ -137,6 +137,13 @@ class FluxDiT(nn.Module):
             [SingleStreamBlock(p.hidden_size, p.num_heads, p.mlp_ratio) for _ in range(p.depth_single_blocks)])
         self.final_layer = LastLayer(p.hidden_size, 1, p.in_channels)
 
+    def set_sequence_parallel(self, sp) -> None:
+        """Shard tokens over the ranks of `sp` (a parallel.SequenceParallel, or None to undo):
+        callers then pass each rank its slice of img, txt and of the RoPE table
+        (parallel.shard_joint_sequence) and get that rank's slice of the output."""
+        for blk in list(self.double_blocks) + list(self.single_blocks):
+            blk.sequence_parallel = sp
+
     def forward(self, img: Tensor, txt: Tensor, timesteps: Tensor, guidance: Tensor | None, pe: Tensor) -> Tensor:
         """`pe` is the RoPE table of the joint (text first, then image) sequence, e.g.
         `self.pe_embedder(torch.cat((txt_ids, img_ids), 1))`; it does not change between

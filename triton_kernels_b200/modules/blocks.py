@@ -76,10 +76,8 @@ class SelfAttention(nn.Module):
     def forward(self, x: Tensor, pe: Tensor) -> Tensor:
         B, L, C = x.shape
         qkv = self.qkv(x)
-        q, k, v = _assemble_qkv([(qkv, self.norm)], pe, self.num_heads)
         attn = torch.empty((B, L, C), device=x.device, dtype=x.dtype)
-        D = C // self.num_heads
-        attention_into(q, k, v, attn.view(B, L, self.num_heads, D).permute(0, 2, 1, 3), D**-0.5)
+        _joint_attention([(qkv, self.norm)], pe, self.num_heads, (C // self.num_heads) ** -0.5, attn)
         return self.proj(attn)
 
 
@@ -117,8 +115,7 @@ def _assemble_qkv(streams, pe: Tensor, num_heads: int):
     """streams: [(packed projection [B, L_s, >= 3C], QKNorm module)], first stream's tokens first."""
     B = streams[0][0].shape[0]
     L = sum(s.shape[1] for s, _ in streams)
-    C3 = 3 * streams[0][1].query_norm.scale.shape[0] * num_heads
-    D = C3 // (3 * num_heads)
+    D = streams[0][1].query_norm.scale.shape[0]
     dev, dt = streams[0][0].device, streams[0][0].dtype
     q = torch.empty((B, num_heads, L, D), device=dev, dtype=dt)
     k = torch.empty_like(q)
@@ -126,6 +123,35 @@ def _assemble_qkv(streams, pe: Tensor, num_heads: int):
     args = [(s, n.query_norm.scale.to(dt), n.key_norm.scale.to(dt)) for s, n in streams]
     qkv_prepare_into(args, pe, q, k, v, num_heads, eps=1e-6)
     return q, k, v
+
+
+def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Tensor, sp=None) -> None:
+    """q/k/v assembly (split, QK-RMSNorm, RoPE, stream concat) + attention, written into `out`,
+    a [B, L, C] view with unit stride on the last dim (it may be a column range of a wider
+    buffer).  With a SequenceParallel handle the local tokens are exchanged for the local
+    heads before attention and back after it (triton_kernels_b200/parallel/ulysses.py)."""
+    if sp is None or sp.world == 1:
+        q, k, v = _assemble_qkv(streams, pe, num_heads)
+        B, H, L, D = q.shape
+        attention_into(q, k, v, out.unflatten(2, (H, D)).permute(0, 2, 1, 3), scale)
+        return
+    B = streams[0][0].shape[0]
+    L_loc = sum(s.shape[1] for s, _ in streams)
+    D = streams[0][1].query_norm.scale.shape[0]
+    dev, dt = streams[0][0].device, streams[0][0].dtype
+    shape, layout = sp.send_layout(B, L_loc, num_heads, D)
+    Hp = layout[0]
+    send = torch.empty(shape, device=dev, dtype=dt)
+    flat = send.view(-1)
+    args = [(s, n.query_norm.scale.to(dt), n.key_norm.scale.to(dt)) for s, n in streams]
+    qkv_prepare_into(args, pe, flat, flat[Hp * D :], flat[2 * Hp * D :], num_heads, eps=1e-6, out_layout=layout,
+                     head_dim=D)
+    full = sp.tokens_to_heads(send)  # [B, L, 3, Hp, D]
+    L = full.shape[1]
+    o = torch.empty((B, L, Hp * D), device=dev, dtype=dt)
+    qv, kv, vv = (full[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [B, Hp, L, D] views
+    attention_into(qv, kv, vv, o.view(B, L, Hp, D).permute(0, 2, 1, 3), scale)
+    sp.heads_to_tokens(o, out)
 
 
 def _ln_mod(x: Tensor, packed_mod: Tensor, chunk_shift: int) -> Tensor:
@@ -167,6 +193,7 @@ class SingleStreamBlock(nn.Module):
         self.norm = QKNorm(head_dim)
         self.mlp_act = nn.GELU(approximate="tanh")
         self.modulation = Modulation(hidden_size, double=False)
+        self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
 
     def forward(self, x: Tensor, vec: Tensor, pe: Tensor) -> Tensor:
         _check_inputs(x, vec)
@@ -190,8 +217,7 @@ class SingleStreamBlock(nn.Module):
             linear_into(x_mod.view(B * L, C), w[: 3 * C], b[: 3 * C], qkv.view(B * L, 3 * C))
             linear_into(x_mod.view(B * L, C), w[3 * C :], b[3 * C :], cat.view(B * L, C + M)[:, C:], epi=_lib.EPI_GELU)
 
-        q, k, v = _assemble_qkv([(qkv, self.norm)], pe, H)
-        attention_into(q, k, v, cat.view(B, L, -1)[:, :, :C].unflatten(2, (H, D)).permute(0, 2, 1, 3), self.scale)
+        _joint_attention([(qkv, self.norm)], pe, H, self.scale, cat[:, :, :C], self.sequence_parallel)
 
         out = torch.empty_like(x)
         _gated_linear(cat.view(B * L, C + M), self.linear2, x.view(B * L, C), mod[:, 2 * C : 3 * C], L, out.view(B * L, C))
@@ -213,6 +239,7 @@ class DoubleStreamBlock(nn.Module):
         self.txt_mod = Modulation(hidden_size, double=True)
         self.txt_attn = SelfAttention(dim=hidden_size, num_heads=num_heads, qkv_bias=qkv_bias)
         self.txt_mlp = MLP(hidden_size, mlp_hidden_dim)
+        self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
 
     def _stream_tail(self, x: Tensor, attn: Tensor, row0: int, mod: Tensor, sa: SelfAttention, mlp: nn.Sequential) -> Tensor:
         """proj + gate/residual, LN+mod2, MLP up (GELU), MLP down + gate/residual for one stream.
@@ -245,9 +272,9 @@ class DoubleStreamBlock(nn.Module):
 
         img_qkv = qkv_of(img, img_mod, self.img_attn)
         txt_qkv = qkv_of(txt, txt_mod, self.txt_attn)
-        q, k, v = _assemble_qkv([(txt_qkv, self.txt_attn.norm), (img_qkv, self.img_attn.norm)], pe, H)
         attn = torch.empty((B, Lt + Li, C), device=img.device, dtype=img.dtype)
-        attention_into(q, k, v, attn.view(B, Lt + Li, H, D).permute(0, 2, 1, 3), D**-0.5)
+        _joint_attention([(txt_qkv, self.txt_attn.norm), (img_qkv, self.img_attn.norm)], pe, H, D**-0.5, attn,
+                         self.sequence_parallel)
 
         img_out = self._stream_tail(img, attn, Lt, img_mod, self.img_attn, self.img_mlp)
         txt_out = self._stream_tail(txt, attn, 0, txt_mod, self.txt_attn, self.txt_mlp)

@@ -94,24 +94,30 @@ def qkv_prepare_into(
     v: torch.Tensor,
     num_heads: int,
     eps: float = 1e-6,
+    out_layout: tuple[int, int, int, int, int] | None = None,
+    head_dim: int | None = None,
 ) -> None:
     """streams: one or two (src [B, L_s, >=3*H*D] with unit column stride, q_scale, k_scale);
-    q,k,v: contiguous [B,H,L,D] outputs with L = sum L_s."""
+    q,k,v: outputs with L = sum L_s rows per (batch, head).  By default they are contiguous
+    [B,H,L,D]; `out_layout` = (heads_per_group, batch stride, group stride, head stride, row
+    stride) in elements addresses them as b*sb + (h // hpg)*sg + (h % hpg)*sh + l*sl instead."""
     assert 1 <= len(streams) <= 2
     B = streams[0][0].shape[0]
-    D = q.shape[-1]
+    D = head_dim if head_dim is not None else q.shape[-1]
     args = []
     for src, qs, ks in streams:
-        assert src.stride(2) == 1 and src.stride(0) == src.shape[1] * src.stride(1)
+        assert src.stride(2) == 1 and (src.shape[0] == 1 or src.stride(0) == src.shape[1] * src.stride(1))
         args += [_lib.ptr(src), src.shape[1], src.stride(1), _lib.ptr(qs), _lib.ptr(ks)]
     if len(streams) == 1:
         args += [None, 0, 0, None, None]
     pe_c = None
     if pe is not None:
-        pe_c = pe.to(torch.float32).contiguous()
+        pe_c = pe if (pe.dtype == torch.float32 and pe.is_contiguous()) else pe.to(torch.float32).contiguous()
+    layout = out_layout if out_layout is not None else (0, 0, 0, 0, 0)
     _lib.check(
         _lib.load().fluxb_qkv_prep(
-            *args, _lib.ptr(pe_c), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), B, num_heads, D, eps, _lib.stream_handle()
+            *args, _lib.ptr(pe_c), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), B, num_heads, D, *layout, eps,
+            _lib.stream_handle()
         )
     )
 

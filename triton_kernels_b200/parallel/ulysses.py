@@ -1,0 +1,88 @@
+"""Ulysses sequence parallelism for the joint attention of the Flux blocks.
+
+Every rank holds L/P tokens of each stream and runs LayerNorm, all GEMMs, QK-norm and RoPE on
+them for all H heads.  Around attention the sharding is switched from tokens to heads:
+
+  send   [P, B, L_loc, 3, H/P, D]   written directly by the q/k/v assembly kernel: chunk g holds
+                                     this rank's tokens for the heads of rank g, q|k|v
+                                     interleaved per token
+  all-to-all (equal splits, one call for q, k and v together)
+  recv   [P, B, L_loc, 3, H/P, D]   chunk s = tokens of rank s; with B = 1 this IS the full
+                                     sequence [L, 3, H/P, D], token-major, and the attention
+                                     kernel reads q, k, v from it through strides (no copy)
+  attention over all L tokens for the local H/P heads -> [B, L, (H/P)*D]
+  all-to-all back (chunk s = the rows rank s owns), then one strided copy interleaves the head
+  groups into [B, L_loc, H*D].
+
+Softmax attention does not depend on the order of the keys, and each query row is independent,
+so the gathered order (rank-major: txt_0 img_0 txt_1 img_1 ...) need not equal the single-GPU
+order (all text, then all image) as long as RoPE was applied with each token's own table row
+before the exchange — which is how the assembly kernel is called.
+
+The exchange functions are plain torch.distributed calls on whatever device the tensors live
+on, so the layout logic is exercised on CPU ranks (gloo) as well as on GPUs (NCCL).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+
+class SequenceParallel:
+    """Process-group handle plus the two layout-changing exchanges."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+
+    # ---- token-sharded -> head-sharded -------------------------------------------------
+    def send_layout(self, B: int, L_loc: int, H: int, D: int) -> tuple[tuple[int, ...], tuple[int, int, int, int, int]]:
+        """Shape of the send buffer and the (heads_per_group, batch, group, head, row) strides
+        with which q (offset 0), k (offset Hp*D) and v (offset 2*Hp*D) are written into it."""
+        P = self.world
+        assert H % P == 0, f"{H} heads cannot be split over {P} ranks"
+        Hp = H // P
+        shape = (P, B, L_loc, 3, Hp, D)
+        row = 3 * Hp * D
+        return shape, (Hp, L_loc * row, B * L_loc * row, D, row)
+
+    def tokens_to_heads(self, send: Tensor) -> Tensor:
+        """send [P, B, L_loc, 3, Hp, D] -> [B, L, 3, Hp, D] with L = P*L_loc (rows ordered by
+        source rank).  A view of the receive buffer when B == 1."""
+        P, B, L_loc = send.shape[:3]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        if B == 1:
+            return recv.view(1, P * L_loc, *send.shape[3:])
+        return recv.permute(1, 0, 2, 3, 4, 5).reshape(B, P * L_loc, *send.shape[3:])
+
+    # ---- head-sharded -> token-sharded -------------------------------------------------
+    def heads_to_tokens(self, o: Tensor, out: Tensor | None = None) -> Tensor:
+        """o [B, L, Hp*D] (rows ordered by owning rank) -> [B, L_loc, H*D] for the local rows.
+        `out` may be any [B, L_loc, H*D] view with unit stride on the last dim."""
+        P = self.world
+        B, L, W = o.shape
+        L_loc = L // P
+        send = o.view(B, P, L_loc, W).permute(1, 0, 2, 3)
+        send = send.contiguous() if B > 1 else send.reshape(P, 1, L_loc, W)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        if out is None:
+            out = torch.empty((B, L_loc, P * W), device=o.device, dtype=o.dtype)
+        out.unflatten(2, (P, W)).copy_(recv.permute(1, 2, 0, 3))
+        return out
+
+
+def shard_joint_sequence(txt: Tensor, img: Tensor, pe: Tensor, rank: int, world: int):
+    """This rank's slice of both streams and the matching rows of the RoPE table.
+
+    txt [B, Lt, *], img [B, Li, *], pe [1, 1, Lt + Li, D/2, 2, 2] (text rows first).  Returns
+    (txt_loc, img_loc, pe_loc) with pe_loc ordered text-then-image like the local sequence."""
+    Lt, Li = txt.shape[1], img.shape[1]
+    assert Lt % world == 0 and Li % world == 0, "both stream lengths must be divisible by the number of ranks"
+    t0, t1 = rank * (Lt // world), (rank + 1) * (Lt // world)
+    i0, i1 = rank * (Li // world), (rank + 1) * (Li // world)
+    pe_loc = torch.cat((pe[:, :, t0:t1], pe[:, :, Lt + i0 : Lt + i1]), dim=2).contiguous()
+    return txt[:, t0:t1].contiguous(), img[:, i0:i1].contiguous(), pe_loc
