@@ -66,6 +66,31 @@ int fluxb_linear(const void* x, const void* w, const void* bias, void* y, int64_
                  fluxb_stream_t stream);
 
 /*
+ * Up to four linears that share N, K and the epilogue but have their own operands, outputs
+ * and row counts, run as ONE launch (their tiles share the persistent grid).  The double-stream
+ * block uses it to run the image-stream and text-stream projections together: alone, the
+ * 512-token text GEMMs fill a third of the SMs.  Replaces pairs of calls such as
+ * triton_kernels/modules/blocks.py:147+153, 166+170 and the two MLPs at :167-171.
+ * Fields have the meaning of the fluxb_linear arguments of the same name.
+ */
+typedef struct {
+  const void* x;
+  const void* w;
+  const void* bias;
+  void* y;
+  int64_t M, ldx, ldw, ldy;
+  void* y2;
+  int64_t ldy2;
+  const void* resid;
+  int64_t ldr;
+  const void* gate;
+  int64_t gate_stride, rows_per_batch;
+} fluxb_linear_problem;
+int fluxb_linear_grouped(const fluxb_linear_problem* problems, int count, int64_t N, int64_t K,
+                         int epi, int64_t split, int epi2, int round_before_act,
+                         fluxb_stream_t stream);
+
+/*
  * out[b, n] = sum_k silu(vec[b,k]) * w[n,k] + bias[n]  for small b (<= 8): the adaLN
  * modulation projection.  Replaces `Modulation.forward`, triton_kernels/modules/blocks.py:61-67
  * (F.silu + tk.linear with M = batch) and triton_kernels/ops/silu.py:5-13 as its prologue.

@@ -20,11 +20,25 @@ ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT = -1, -2, -3, -4
 
 # name -> (restype, argtypes); mirrors include/fluxb200.h one to one.
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
+
+
+class LinearProblem(ctypes.Structure):
+    """fluxb_linear_problem of include/fluxb200.h."""
+
+    _fields_ = [
+        ("x", _P), ("w", _P), ("bias", _P), ("y", _P),
+        ("M", _L), ("ldx", _L), ("ldw", _L), ("ldy", _L),
+        ("y2", _P), ("ldy2", _L), ("resid", _P), ("ldr", _L),
+        ("gate", _P), ("gate_stride", _L), ("rows_per_batch", _L),
+    ]
+
+
 SIGNATURES = {
     "fluxb_version": (_I, []),
     "fluxb_last_error": (c_char_p, []),
     "fluxb_device_status_read": (_I, [POINTER(c_int)]),
     "fluxb_linear": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _L, _L, _I, _P, _L, _P, _L, _L, _I, _P]),
+    "fluxb_linear_grouped": (_I, [POINTER(LinearProblem), _I, _L, _L, _I, _L, _I, _I, _P]),
     "fluxb_modulation_gemv": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _P]),
     "fluxb_attention": (_I, [_P, _P, _P, _P] + [_L] * 5 + [_L] * 12 + [_F, _P]),
     "fluxb_layer_norm_modulation": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _F, _I, _P]),

@@ -277,10 +277,35 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int MAX_PROBLEMS = 4;
+
+// Up to four GEMMs that differ in operands, outputs and row counts run as ONE persistent
+// launch: their tiles are concatenated (problem 0's tiles first) and dealt round-robin to the
+// CTA pairs.  A small problem (the 512-token text stream) would fill a third of the machine on
+// its own; riding along with the image stream's GEMM it fills the tail of that launch instead.
+struct Problem {
+  CUtensorMap tm_a, tm_b;
+  Params p;
+  int tile_start;  // index of this problem's first tile in the concatenated order
+  int tiles_m;     // 256-row blocks
+};
+struct Grouped {
+  Problem prob[MAX_PROBLEMS];
+  int count;
+  int total_tiles;
+  int pair_stages;
+};
+
+__device__ __forceinline__ int find_problem(const Grouped& g, int tile) {
+  int i = 0;
+#pragma unroll
+  for (int k = 1; k < MAX_PROBLEMS; ++k)
+    if (k < g.count && tile >= g.prob[k].tile_start) i = k;
+  return i;
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 const Params p) {
+gemm_pair_kernel(const __grid_constant__ Grouped g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -297,9 +322,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_kb = (p.K + BK - 1) / BK;
-  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-  const int num_tiles = tiles_m * p.tiles_n;
+  const int num_tiles = g.total_tiles;
+  DeviceStatus* const status = g.prob[0].p.status;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -312,8 +336,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tm_a);
-    tma_prefetch_desc(&tm_b);
+    for (int i = 0; i < g.count; ++i) {
+      tma_prefetch_desc(&g.prob[i].tm_a);
+      tma_prefetch_desc(&g.prob[i].tm_b);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, TMEM_COLS);
@@ -331,18 +357,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
+        const Problem& pr = g.prob[find_problem(g, tile)];
+        const Params& p = pr.p;
+        const int num_kb = (p.K + BK - 1) / BK;
         int m_blk, n_blk;
-        tile_coords(p, tile, tiles_m, m_blk, n_blk);
+        tile_coords(p, tile - pr.tile_start, pr.tiles_m, m_blk, n_blk);
         const int row0 = m_blk * 2 * BM + (int)rank * BM;
         const int col0 = n_blk * BN + (int)rank * BNH;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1, abort_flag, p.status, 41)) { ok = false; break; }
+          if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1, abort_flag, status, 41)) { ok = false; break; }
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
           const uint32_t full_addr = map_to_cta(smem_u32(&full_bar[stage]), 0);
           uint8_t* a_dst = smem + stage * STAGE_BYTES;
-          tma_load_2d_pair(a_dst, &tm_a, full_addr, kb * BK, row0);
-          tma_load_2d_pair(a_dst + A_BYTES, &tm_b, full_addr, kb * BK, col0);
-          if (++stage == p.pair_stages) { stage = 0; phase ^= 1; }
+          tma_load_2d_pair(a_dst, &pr.tm_a, full_addr, kb * BK, row0);
+          tma_load_2d_pair(a_dst + A_BYTES, &pr.tm_b, full_addr, kb * BK, col0);
+          if (++stage == g.pair_stages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -355,13 +384,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       bool ok = true;
       int local = 0;
       for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
+        const int num_kb = (g.prob[find_problem(g, tile)].p.K + BK - 1) / BK;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 43)) { ok = false; break; }
+        if (!mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, 43)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag, p.status, 44)) { ok = false; break; }
+          if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag, status, 44)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
@@ -370,7 +400,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           for (int k = 0; k < BK / 16; ++k)
             umma_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair_both(&empty_bar[stage]);
-          if (++stage == p.pair_stages) { stage = 0; phase ^= 1; }
+          if (++stage == g.pair_stages) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit_pair_both(&acc_full[acc]);
       }
@@ -382,11 +412,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     bool ok = true;
     const uint32_t acc_empty_leader0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
     for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
+      const Problem& pr = g.prob[find_problem(g, tile)];
+      const Params& p = pr.p;
       int m_blk, n_blk;
-      tile_coords(p, tile, tiles_m, m_blk, n_blk);
+      tile_coords(p, tile - pr.tile_start, pr.tiles_m, m_blk, n_blk);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      if (!mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, p.status, 45)) { ok = false; break; }
+      if (!mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, status, 45)) { ok = false; break; }
       tc_fence_after_sync();
       const int row = m_blk * 2 * BM + (int)rank * BM + quad * 32 + lane;
       const int n0 = n_blk * BN;
@@ -422,77 +454,74 @@ using namespace fluxb;
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void* y, int64_t M,
-                            int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int epi,
-                            void* y2, int64_t ldy2, int64_t split, int epi2, const void* resid,
-                            int64_t ldr, const void* gate, int64_t gate_stride,
-                            int64_t rows_per_batch, int round_before_act, fluxb_stream_t stream) {
+static bool use_pair_kernel() {
+  // CTA pairs (256x256 tiles) unless FLUXB_GEMM_PAIR=0 asks for the single-CTA kernel.
+  static const int pair_env = [] {
+    const char* s = getenv("FLUXB_GEMM_PAIR");
+    return (s != nullptr && *s != 0) ? atoi(s) : 1;
+  }();
+  return pair_env != 0;
+}
+
+// Validates one problem, encodes its tensor maps and fills its kernel parameters.
+static int prepare_problem(const fluxb_linear_problem& a, int64_t N, int64_t K, int epi, int64_t split, int epi2,
+                           int round_before_act, bool use_pair, CUtensorMap* tm_a, CUtensorMap* tm_b,
+                           fluxb::gemm::Params* out) {
   using namespace fluxb::gemm;
-  if (M < 0 || N < 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: bad sizes");
-  if (M == 0 || N == 0) return FLUXB_OK;
+  const int64_t M = a.M;
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: bad sizes");
   if (M > INT32_MAX / 2 || N > INT32_MAX / 2 || K > INT32_MAX / 2)
     return set_error(FLUXB_ERR_UNSUPPORTED, "linear: dimension too large");
-  if (!x || !w || !y) return set_error(FLUXB_ERR_BAD_ARG, "linear: null pointer");
+  if (!a.x || !a.w || !a.y) return set_error(FLUXB_ERR_BAD_ARG, "linear: null pointer");
   if (split < 0 || split > N) return set_error(FLUXB_ERR_BAD_ARG, "linear: split outside [0, N]");
   if (split < N) {
-    if (!y2) return set_error(FLUXB_ERR_BAD_ARG, "linear: split < N needs a second output");
+    if (!a.y2) return set_error(FLUXB_ERR_BAD_ARG, "linear: split < N needs a second output");
     if (split % BN) return set_error(FLUXB_ERR_BAD_ARG, "linear: split must be a multiple of %d", BN);
-    if (ldy2 % 8 || !aligned16(y2)) return set_error(FLUXB_ERR_BAD_ARG, "linear: second output misaligned");
+    if (a.ldy2 % 8 || !aligned16(a.y2)) return set_error(FLUXB_ERR_BAD_ARG, "linear: second output misaligned");
   }
-  if (K % 8 || ldx % 8 || ldw % 8 || N % 8 || ldy % 8 || ldx < K || ldw < K)
+  if (K % 8 || a.ldx % 8 || a.ldw % 8 || N % 8 || a.ldy % 8 || a.ldx < K || a.ldw < K)
     return set_error(FLUXB_ERR_BAD_ARG, "linear: K, N and row strides must be multiples of 8 (and strides >= K)");
-  if (!aligned16(x) || !aligned16(w) || !aligned16(y) || !aligned16(bias))
+  if (!aligned16(a.x) || !aligned16(a.w) || !aligned16(a.y) || !aligned16(a.bias))
     return set_error(FLUXB_ERR_BAD_ARG, "linear: pointers must be 16-byte aligned");
   const int epis[2] = {epi, split < N ? epi2 : FLUXB_EPI_NONE};
   for (int e : epis) {
     if (e != FLUXB_EPI_NONE && e != FLUXB_EPI_GELU && e != FLUXB_EPI_GATE_RESID)
       return set_error(FLUXB_ERR_UNSUPPORTED, "linear: unknown epilogue %d", e);
     if (e == FLUXB_EPI_GATE_RESID) {
-      if (!resid || !gate || rows_per_batch <= 0 || ldr % 8 || gate_stride % 8 || !aligned16(resid) ||
-          !aligned16(gate))
+      if (!a.resid || !a.gate || a.rows_per_batch <= 0 || a.ldr % 8 || a.gate_stride % 8 || !aligned16(a.resid) ||
+          !aligned16(a.gate))
         return set_error(FLUXB_ERR_BAD_ARG, "linear: gate/residual epilogue needs aligned resid, gate and rows_per_batch > 0");
     }
   }
-
-  // Kernel choice: CTA pairs (256x256 tiles) unless FLUXB_GEMM_PAIR=0 asks for the single-CTA kernel.
-  static const int pair_env = [] {
-    const char* s = getenv("FLUXB_GEMM_PAIR");
-    return (s != nullptr && *s != 0) ? atoi(s) : 1;
-  }();
-  const bool use_pair = pair_env != 0;
-
-  CUtensorMap tm_a, tm_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
-    const uint64_t strides[1] = {(uint64_t)ldx * 2};
+    const uint64_t strides[1] = {(uint64_t)a.ldx * 2};
     const uint32_t box[2] = {BK, BM};
-    int rc = encode_tmap_bf16(&tm_a, x, 2, dims, strides, box);
+    int rc = encode_tmap_bf16(tm_a, a.x, 2, dims, strides, box);
     if (rc != FLUXB_OK) return rc;
   }
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
-    const uint64_t strides[1] = {(uint64_t)ldw * 2};
+    const uint64_t strides[1] = {(uint64_t)a.ldw * 2};
     const uint32_t box[2] = {BK, (uint32_t)(use_pair ? fluxb::gemm2::BNH : BN)};
-    int rc = encode_tmap_bf16(&tm_b, w, 2, dims, strides, box);
+    int rc = encode_tmap_bf16(tm_b, a.w, 2, dims, strides, box);
     if (rc != FLUXB_OK) return rc;
   }
-
-  Params p;
-  p.bias = static_cast<const __nv_bfloat16*>(bias);
-  p.y = static_cast<__nv_bfloat16*>(y);
-  p.y2 = static_cast<__nv_bfloat16*>(y2);
-  p.resid = static_cast<const __nv_bfloat16*>(resid);
-  p.gate = static_cast<const __nv_bfloat16*>(gate);
-  p.ldy = ldy; p.ldy2 = ldy2; p.ldr = ldr; p.gate_stride = gate_stride;
-  p.rows_per_batch = rows_per_batch > 0 ? rows_per_batch : 1;
+  Params& p = *out;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  p.y = static_cast<__nv_bfloat16*>(a.y);
+  p.y2 = static_cast<__nv_bfloat16*>(a.y2);
+  p.resid = static_cast<const __nv_bfloat16*>(a.resid);
+  p.gate = static_cast<const __nv_bfloat16*>(a.gate);
+  p.ldy = a.ldy; p.ldy2 = a.ldy2; p.ldr = a.ldr; p.gate_stride = a.gate_stride;
+  p.rows_per_batch = a.rows_per_batch > 0 ? a.rows_per_batch : 1;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.split = (int)split; p.epi = epi; p.epi2 = epi2; p.round_before_act = round_before_act;
   p.tiles_m = (int)((M + BM - 1) / BM);
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.status = device_status_ptr();
-  static const int stages_env = [] { const char* s = getenv("FLUXB_GEMM_PAIR_STAGES"); return (s && *s) ? atoi(s) : fluxb::gemm2::STAGES; }();
-  p.pair_stages = stages_env < 2 ? 2 : (stages_env > fluxb::gemm2::STAGES ? fluxb::gemm2::STAGES : stages_env);
+  p.pair_stages = fluxb::gemm2::STAGES;
   {
     // Keep the smaller operand resident in L2 when it fits, sweep the larger one.
     const int row_blk = use_pair ? 256 : 128;
@@ -515,22 +544,63 @@ extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void
     }
     if (p.raster_group < 1) p.raster_group = 1;
   }
+  return FLUXB_OK;
+}
 
-  if (use_pair) {
+extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int count, int64_t N, int64_t K, int epi,
+                                    int64_t split, int epi2, int round_before_act, fluxb_stream_t stream) {
+  using namespace fluxb::gemm;
+  if (count < 0 || (count > 0 && problems == nullptr)) return set_error(FLUXB_ERR_BAD_ARG, "linear_grouped: bad problem list");
+  if (count > fluxb::gemm2::MAX_PROBLEMS)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "linear_grouped: at most %d problems per launch", fluxb::gemm2::MAX_PROBLEMS);
+  if (N < 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: bad sizes");
+  const bool use_pair = use_pair_kernel();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  fluxb::gemm2::Grouped g;
+  g.count = 0;
+  g.total_tiles = 0;
+  static const int stages_env = [] { const char* s = getenv("FLUXB_GEMM_PAIR_STAGES"); return (s && *s) ? atoi(s) : fluxb::gemm2::STAGES; }();
+  g.pair_stages = stages_env < 2 ? 2 : (stages_env > fluxb::gemm2::STAGES ? fluxb::gemm2::STAGES : stages_env);
+  for (int i = 0; i < count; ++i) {
+    if (problems[i].M < 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: negative M");
+    if (problems[i].M == 0 || N == 0) continue;  // nothing to compute for this one
+    fluxb::gemm2::Problem& pr = g.prob[g.count];
+    int rc = prepare_problem(problems[i], N, K, epi, split, epi2, round_before_act, use_pair, &pr.tm_a, &pr.tm_b, &pr.p);
+    if (rc != FLUXB_OK) return rc;
+    if (!use_pair) {  // single-CTA kernel: one launch per problem
+      cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
+      const int grid = pr.p.num_tiles < sm_count() ? pr.p.num_tiles : sm_count();
+      gemm_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(pr.tm_a, pr.tm_b, pr.p);
+      continue;
+    }
+    pr.tiles_m = (int)((problems[i].M + 255) / 256);
+    pr.tile_start = g.total_tiles;
+    g.total_tiles += pr.tiles_m * pr.p.tiles_n;
+    ++g.count;
+  }
+  if (use_pair && g.count > 0) {
     cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          fluxb::gemm2::SMEM_BYTES);
     if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
-    const int tiles = (int)((M + 255) / 256) * p.tiles_n;
-    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
-    fluxb::gemm2::gemm_pair_kernel<<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES,
-                                     static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
-  } else {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
-    const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
-    gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+    const int pairs = g.total_tiles < sm_count() / 2 ? g.total_tiles : sm_count() / 2;
+    fluxb::gemm2::gemm_pair_kernel<<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
+}
+
+extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void* y, int64_t M,
+                            int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldy, int epi,
+                            void* y2, int64_t ldy2, int64_t split, int epi2, const void* resid,
+                            int64_t ldr, const void* gate, int64_t gate_stride,
+                            int64_t rows_per_batch, int round_before_act, fluxb_stream_t stream) {
+  fluxb_linear_problem a;
+  a.x = x; a.w = w; a.bias = bias; a.y = y; a.M = M; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
+  a.y2 = y2; a.ldy2 = ldy2; a.resid = resid; a.ldr = ldr; a.gate = gate; a.gate_stride = gate_stride;
+  a.rows_per_batch = rows_per_batch;
+  if (M < 0 || N < 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: bad sizes");
+  return fluxb_linear_grouped(&a, 1, N, K, epi, split, epi2, round_before_act, stream);
 }

@@ -58,6 +58,49 @@ def linear_into(
         launch_probe.append((M, N, K, ev0, ev1))
 
 
+def linear_grouped_into(
+    problems: list[dict],
+    *,
+    epi: int = _lib.EPI_NONE,
+    split: int | None = None,
+    epi2: int = _lib.EPI_NONE,
+    round_before_act: bool = False,
+) -> None:
+    """Several linears with the same N, K and epilogue in ONE launch (fluxb_linear_grouped).
+    Each problem is a dict with the keyword names of `linear_into`: x2d, w, b, y and optionally
+    y2, resid, gate, gate_stride, rows_per_batch.  At most four problems per launch; longer
+    lists are cut into launches of four."""
+    if not problems:
+        return
+    N, K = problems[0]["w"].shape
+    if split is None:
+        split = N
+    for lo in range(0, len(problems), 4):
+        chunk = problems[lo : lo + 4]
+        arr = (_lib.LinearProblem * len(chunk))()
+        for slot, pr in zip(arr, chunk):
+            x2d, w, y = pr["x2d"], pr["w"], pr["y"]
+            assert tuple(w.shape) == (N, K) and x2d.shape[1] == K
+            assert x2d.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1
+            y2, resid, gate = pr.get("y2"), pr.get("resid"), pr.get("gate")
+            slot.x, slot.w, slot.bias, slot.y = _lib.ptr(x2d), _lib.ptr(w), _lib.ptr(pr.get("b")), _lib.ptr(y)
+            slot.M, slot.ldx, slot.ldw, slot.ldy = x2d.shape[0], x2d.stride(0), w.stride(0), y.stride(0)
+            slot.y2, slot.ldy2 = _lib.ptr(y2), (y2.stride(0) if y2 is not None else 0)
+            slot.resid, slot.ldr = _lib.ptr(resid), (resid.stride(0) if resid is not None else 0)
+            slot.gate, slot.gate_stride = _lib.ptr(gate), pr.get("gate_stride", 0)
+            slot.rows_per_batch = pr.get("rows_per_batch", 1)
+        if launch_probe is not None:
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        _lib.check(
+            _lib.load().fluxb_linear_grouped(arr, len(chunk), N, K, epi, split, epi2, int(round_before_act), _lib.stream_handle())
+        )
+        if launch_probe is not None:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            launch_probe.append((tuple(pr["x2d"].shape[0] for pr in chunk), N, K, ev0, ev1))
+
+
 def _as_2d(x: torch.Tensor, K: int) -> torch.Tensor:
     x2d = x.reshape(-1, K)
     if x2d.stride(1) != 1 or x2d.stride(0) % 8 or x2d.data_ptr() % 16:

@@ -28,7 +28,7 @@ from torch import Tensor, nn
 
 from triton_kernels_b200 import _lib
 from triton_kernels_b200.kernels.attention import attention_into, scaled_dot_product_attention
-from triton_kernels_b200.kernels.linear import linear, linear_into
+from triton_kernels_b200.kernels.linear import linear, linear_grouped_into, linear_into
 from triton_kernels_b200.kernels.normalization import layer_norm_modulation_into
 from triton_kernels_b200.kernels.positional_embedding import apply_rope
 from triton_kernels_b200.modules.normalization import QKNorm
@@ -241,21 +241,6 @@ class DoubleStreamBlock(nn.Module):
         self.txt_mlp = MLP(hidden_size, mlp_hidden_dim)
         self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
 
-    def _stream_tail(self, x: Tensor, attn: Tensor, row0: int, mod: Tensor, sa: SelfAttention, mlp: nn.Sequential) -> Tensor:
-        """proj + gate/residual, LN+mod2, MLP up (GELU), MLP down + gate/residual for one stream.
-        `attn` is the joint [B, L, C] attention output; this stream's rows start at row0."""
-        B, Ls, C = x.shape
-        L = attn.shape[1]
-        x1 = torch.empty_like(x)
-        for b in range(B):  # the stream's rows of each batch item are one strided 2-D block
-            _gated_linear(attn[b, row0 : row0 + Ls], sa.proj, x[b], mod[b : b + 1, 2 * C : 3 * C], Ls, x1[b])
-        h = _ln_mod(x1, mod, 3)
-        up = torch.empty((B * Ls, mlp[0].out_features), device=x.device, dtype=x.dtype)
-        linear_into(h.view(B * Ls, C), mlp[0].weight, mlp[0].bias, up, epi=_lib.EPI_GELU)
-        out = torch.empty_like(x)
-        _gated_linear(up, mlp[2], x1.view(B * Ls, C), mod[:, 5 * C : 6 * C], Ls, out.view(B * Ls, C))
-        return out
-
     def forward(self, img: Tensor, txt: Tensor, vec: Tensor, pe: Tensor) -> tuple[Tensor, Tensor]:
         _check_inputs(img, txt, vec)
         img, txt = img.contiguous(), txt.contiguous()
@@ -263,19 +248,51 @@ class DoubleStreamBlock(nn.Module):
         Lt = txt.shape[1]
         H = self.num_heads
         D = C // H
-        img_mod = self.img_mod.packed(vec)  # [B, 6C]
-        txt_mod = self.txt_mod.packed(vec)
+        dev, dt = img.device, img.dtype
+        # stream order everywhere below: (txt, img), the order of the joint sequence
+        xs = (txt, img)
+        Ls = (Lt, Li)
+        mods = (self.txt_mod.packed(vec), self.img_mod.packed(vec))  # [B, 6C] each
+        attns = (self.txt_attn, self.img_attn)
+        mlps = (self.txt_mlp, self.img_mlp)
 
-        def qkv_of(x, mod, sa):
-            xm = _ln_mod(x, mod, 0)
-            return linear(xm, sa.qkv.weight, sa.qkv.bias)
+        def gate_of(mod, chunk, b=None):
+            g = mod[:, chunk * C : (chunk + 1) * C]
+            return (g, g.stride(0) if B > 1 else 0) if b is None else (g[b : b + 1], 0)
 
-        img_qkv = qkv_of(img, img_mod, self.img_attn)
-        txt_qkv = qkv_of(txt, txt_mod, self.txt_attn)
-        attn = torch.empty((B, Lt + Li, C), device=img.device, dtype=img.dtype)
-        _joint_attention([(txt_qkv, self.txt_attn.norm), (img_qkv, self.img_attn.norm)], pe, H, D**-0.5, attn,
+        # LayerNorm+modulation, then both streams' qkv projections in one launch
+        h1 = [_ln_mod(x, m, 0) for x, m in zip(xs, mods)]
+        qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]
+        linear_grouped_into([
+            dict(x2d=h.view(B * L, C), w=a.qkv.weight, b=a.qkv.bias, y=o.view(B * L, 3 * C))
+            for h, a, o, L in zip(h1, attns, qkvs, Ls)])
+
+        attn = torch.empty((B, Lt + Li, C), device=dev, dtype=dt)
+        _joint_attention([(qkvs[0], self.txt_attn.norm), (qkvs[1], self.img_attn.norm)], pe, H, D**-0.5, attn,
                          self.sequence_parallel)
 
-        img_out = self._stream_tail(img, attn, Lt, img_mod, self.img_attn, self.img_mlp)
-        txt_out = self._stream_tail(txt, attn, 0, txt_mod, self.txt_attn, self.txt_mlp)
-        return img_out, txt_out
+        # proj + gate/residual: the rows of one stream of one batch item are one strided 2-D block
+        x1 = [torch.empty_like(x) for x in xs]
+        row0 = (0, Lt)
+        probs = []
+        for s_ in range(2):
+            for b in range(B):
+                g, gs = gate_of(mods[s_], 2, b)
+                probs.append(dict(x2d=attn[b, row0[s_] : row0[s_] + Ls[s_]], w=attns[s_].proj.weight, b=attns[s_].proj.bias,
+                                  y=x1[s_][b], resid=xs[s_][b], gate=g, gate_stride=gs, rows_per_batch=Ls[s_]))
+        linear_grouped_into(probs, epi=_lib.EPI_GATE_RESID)
+
+        # MLP: LN+mod2, up-projection with GELU, down-projection with gate/residual
+        h2 = [_ln_mod(x, m, 3) for x, m in zip(x1, mods)]
+        ups = [torch.empty((B * L, mlp[0].out_features), device=dev, dtype=dt) for L, mlp in zip(Ls, mlps)]
+        linear_grouped_into([
+            dict(x2d=h.view(B * L, C), w=mlp[0].weight, b=mlp[0].bias, y=u) for h, mlp, u, L in zip(h2, mlps, ups, Ls)],
+            epi=_lib.EPI_GELU)
+        outs = [torch.empty_like(x) for x in xs]
+        probs = []
+        for s_ in range(2):
+            g, gs = gate_of(mods[s_], 5)
+            probs.append(dict(x2d=ups[s_], w=mlps[s_][2].weight, b=mlps[s_][2].bias, y=outs[s_].view(B * Ls[s_], C),
+                              resid=x1[s_].view(B * Ls[s_], C), gate=g, gate_stride=gs, rows_per_batch=Ls[s_]))
+        linear_grouped_into(probs, epi=_lib.EPI_GATE_RESID)
+        return outs[1], outs[0]
