@@ -636,7 +636,7 @@ silu_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n) {
 // shared memory as fp32.
 // ----------------------------------------------------------------------------------------
 template <int BT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512, 2)
 mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __restrict__ w,
                 const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
                 int K, int64_t b0, int apply_silu) {
@@ -650,12 +650,55 @@ mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __re
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  for (int64_t n = (int64_t)blockIdx.x * 8 + warp; n < N; n += (int64_t)gridDim.x * 8) {
+  const int warps = blockDim.x >> 5;
+  // A few persistent blocks per SM; every warp walks output columns with a grid stride, four
+  // 16-byte weight loads in flight per lane.
+  for (int64_t n = (int64_t)blockIdx.x * warps + warp; n < N; n += (int64_t)gridDim.x * warps) {
     const __nv_bfloat16* wr = w + n * K;
     float acc[BT];
 #pragma unroll
     for (int bb = 0; bb < BT; ++bb) acc[bb] = 0.f;
-    for (int k0 = lane * 8; k0 < K; k0 += 256) {
+    int k0 = lane * 8;
+    // Whole 3072-wide rows (the Flux hidden size) are fetched with all twelve 16-byte loads of a
+    // lane in flight at once; other widths go four loads at a time.
+    for (; k0 + 11 * 256 < K; k0 += 12 * 256) {
+      uint4 raw[12];
+#pragma unroll
+      for (int u = 0; u < 12; ++u) raw[u] = __ldg(reinterpret_cast<const uint4*>(wr + k0 + u * 256));
+      // pin the schedule: all twelve loads are issued before the first value is consumed
+#pragma unroll
+      for (int u = 0; u < 12; ++u) forget(raw[u]);
+#pragma unroll
+      for (int u = 0; u < 12; ++u) {
+        Vec<__nv_bfloat16> wv;
+        wv.unpack(raw[u]);
+#pragma unroll
+        for (int bb = 0; bb < BT; ++bb) {
+          const float4 a0 = *reinterpret_cast<const float4*>(sv + bb * K + k0 + u * 256);
+          const float4 a1 = *reinterpret_cast<const float4*>(sv + bb * K + k0 + u * 256 + 4);
+          acc[bb] += wv.v[0] * a0.x + wv.v[1] * a0.y + wv.v[2] * a0.z + wv.v[3] * a0.w +
+                     wv.v[4] * a1.x + wv.v[5] * a1.y + wv.v[6] * a1.z + wv.v[7] * a1.w;
+        }
+      }
+    }
+    for (; k0 + 3 * 256 < K; k0 += 4 * 256) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) raw[u] = __ldg(reinterpret_cast<const uint4*>(wr + k0 + u * 256));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        Vec<__nv_bfloat16> wv;
+        wv.unpack(raw[u]);
+#pragma unroll
+        for (int bb = 0; bb < BT; ++bb) {
+          const float4 a0 = *reinterpret_cast<const float4*>(sv + bb * K + k0 + u * 256);
+          const float4 a1 = *reinterpret_cast<const float4*>(sv + bb * K + k0 + u * 256 + 4);
+          acc[bb] += wv.v[0] * a0.x + wv.v[1] * a0.y + wv.v[2] * a0.z + wv.v[3] * a0.w +
+                     wv.v[4] * a1.x + wv.v[5] * a1.y + wv.v[6] * a1.z + wv.v[7] * a1.w;
+        }
+      }
+    }
+    for (; k0 < K; k0 += 256) {
       Vec<__nv_bfloat16> wv;
       wv.load_nc(wr + k0);
 #pragma unroll
@@ -999,24 +1042,26 @@ extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void*
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
   const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
-  const unsigned grid = (unsigned)((N + 7) / 8 < 148 * 16 ? (N + 7) / 8 : 148 * 16);
+  const int64_t want = (N + 15) / 16;
+  const int64_t cap = (int64_t)sm_count() * 4;
+  const unsigned grid = (unsigned)(want < cap ? want : cap);
   int64_t b0 = 0;
   while (b0 < B) {
     const int64_t left = B - b0;
     if (left >= 4) {
       const size_t smem = (size_t)4 * K * sizeof(float);
       cudaFuncSetAttribute(mod_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      mod_gemv_kernel<4><<<grid, 256, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
+      mod_gemv_kernel<4><<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
       b0 += 4;
     } else if (left >= 2) {
       const size_t smem = (size_t)2 * K * sizeof(float);
       cudaFuncSetAttribute(mod_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      mod_gemv_kernel<2><<<grid, 256, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
+      mod_gemv_kernel<2><<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
       b0 += 2;
     } else {
       const size_t smem = (size_t)K * sizeof(float);
       cudaFuncSetAttribute(mod_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      mod_gemv_kernel<1><<<grid, 256, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
+      mod_gemv_kernel<1><<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
       b0 += 1;
     }
   }
