@@ -259,6 +259,16 @@ def run_micro(which: str, steps: int, warmup: int):
         bufs = [(randn(L, Cc), torch.empty(L, Cc, device=dev, dtype=BF)) for _ in range(sets_for(2 * L * Cc * 2))]
         calls = [lambda x=x, y=y: layer_norm_modulation_into(x, sc, sh, y, L, 1e-6) for x, y in bufs]
         emit("layer_norm_modulation[1,4608,3072]", time_calls(calls), 2 * L * Cc * 2 + 2 * Cc * 2, "hbm")
+        # The same kernel on a problem 16x larger, and a plain device copy of both sizes: a 57 MB
+        # problem is over in ~10 us and cannot reach the bandwidth of a multi-GB stream.
+        Lb = 16 * L
+        xb, yb = randn(Lb, Cc), torch.empty(Lb, Cc, device=dev, dtype=BF)
+        emit("layer_norm_modulation[1,73728,3072]", time_calls([lambda: layer_norm_modulation_into(xb, sc, sh, yb, Lb, 1e-6)]),
+             2 * Lb * Cc * 2, "hbm")
+        emit("device_copy[73728,3072] (torch, for scale)", time_calls([lambda: yb.copy_(xb)]), 2 * Lb * Cc * 2, "hbm")
+        calls = [lambda x=x, y=y: y.copy_(x) for x, y in bufs]
+        emit("device_copy[4608,3072] (torch, for scale)", time_calls(calls), 2 * L * Cc * 2, "hbm")
+        del xb, yb
     if want("rms_norm"):
         w = torch.ones(Cc, device=dev, dtype=BF)
         bufs = [(randn(L, Cc), torch.empty(L, Cc, device=dev, dtype=BF)) for _ in range(sets_for(2 * L * Cc * 2))]

@@ -115,3 +115,34 @@ def test_dit_state_dict_keys_match_oracle_layout():
 
     m = FluxDiT(FluxParams(hidden_size=256, num_heads=2, depth=1, depth_single_blocks=2, context_in_dim=96))
     assert {k: tuple(v.shape) for k, v in m.state_dict().items()} == O.dit_shapes(256, 64, 96, 1, 2)
+
+
+def test_patchify_round_trip_and_schedule():
+    from triton_kernels_b200.flux import get_schedule, patchify, unpatchify
+
+    x = torch.arange(2 * 16 * 8 * 12, dtype=torch.float32).reshape(2, 16, 8, 12)
+    tok = patchify(x)
+    assert tok.shape == (2, 24, 64)
+    # token (h, w) holds channel-major 2x2 patches
+    torch.testing.assert_close(tok[0, 1 * 6 + 2].reshape(16, 2, 2), x[0, :, 2:4, 4:6])
+    torch.testing.assert_close(unpatchify(tok, 8, 12), x)
+    ts = get_schedule(4, 4096)
+    assert len(ts) == 5 and ts[0] == 1.0 and ts[-1] == 0.0 and all(a > b for a, b in zip(ts, ts[1:]))
+    assert get_schedule(4, 4096, shift=False) == [1.0, 0.75, 0.5, 0.25, 0.0]
+    assert ts[2] > 0.5  # shifted towards high noise for long sequences
+
+
+def test_state_dict_loader_reports_missing_and_extra_keys():
+    from oracle import flux_oracle as O
+    from triton_kernels_b200.flux import FluxDiT, FluxParams, load_flux_state_dict
+
+    m = FluxDiT(FluxParams(hidden_size=256, num_heads=2, depth=1, depth_single_blocks=1, context_in_dim=96))
+    g = torch.Generator().manual_seed(3)
+    sd = O.init_params(O.dit_shapes(256, 64, 96, 1, 1), g, bias_std=0.02)
+    sd["vector_in.in_layer.weight"] = torch.zeros(4, 4)
+    with pytest.warns(UserWarning, match="ignoring 1"):
+        load_flux_state_dict(m, sd, dtype=torch.float32)
+    torch.testing.assert_close(m.single_blocks[0].linear1.weight.detach(), sd["single_blocks.0.linear1.weight"])
+    del sd["img_in.bias"]
+    with pytest.raises(KeyError, match="lacks 1"):
+        load_flux_state_dict(m, sd)

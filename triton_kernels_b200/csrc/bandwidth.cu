@@ -76,6 +76,16 @@ __device__ __forceinline__ float group_sum(float v) {
   return v;
 }
 
+// Row addressing through a 3-level stride (head-split views): row -> element offset.
+struct RowAddr {
+  int64_t n1, n2, s0, s1, s2;
+  __device__ __forceinline__ int64_t offset(int64_t row) const {
+    const int64_t i2 = row % n2;
+    const int64_t t = row / n2;
+    return (t / n1) * s0 + (t % n1) * s1 + i2 * s2;
+  }
+};
+
 // ----------------------------------------------------------------------------------------
 // LayerNorm (no affine) + modulation.  G lanes own one row; each lane holds VPL vectors.
 // cols == G * VPL * Vec<T>::N.
@@ -187,6 +197,120 @@ ln_mod_generic_kernel(const T* __restrict__ x, const T* __restrict__ scale,
   }
 }
 
+// ----------------------------------------------------------------------------------------
+// Wide rows (2 KB - 24 KB): the row is fetched by ONE bulk asynchronous copy into shared memory
+// and the three passes read it from there.  A row in flight costs no registers, so every row of
+// a [4608, 3072] problem is resident at once (4 blocks of 8 rows per SM = one wave): all loads
+// are issued in the first microsecond and rows are written back as they complete, instead of
+// two waves of register-resident rows.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Waits (bounded) for this warp's row; returns false if it never arrived.
+__device__ __forceinline__ bool wait_row(uint64_t* bar) {
+  for (uint32_t spin = 0; spin < (1u << 24); ++spin)
+    if (mbar_try_wait(bar, 0)) return true;
+  return false;
+}
+
+template <typename T, bool kLayerNorm>
+__global__ void __launch_bounds__(256, 4)
+norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, const T* __restrict__ shift,
+                      T* __restrict__ y, float* __restrict__ rstd_out, int64_t rows, int cols,
+                      int64_t rows_per_batch, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps) {
+  constexpr int VN = Vec<T>::N;
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t row_bytes = (uint32_t)cols * sizeof(T);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem);  // [8]
+  T* srow = reinterpret_cast<T*>(bulk_smem + 128 + (size_t)warp * row_bytes);
+  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
+  if (row >= rows) return;  // whole warp leaves together; warps never synchronise with each other
+  if (lane == 0) {
+    mbar_init(&bars[warp], 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    mbar_expect_tx(&bars[warp], row_bytes);
+    bulk_load_row(srow, x + xaddr.offset(row), row_bytes, &bars[warp]);
+  }
+  __syncwarp();
+  if (!wait_row(&bars[warp])) return;
+
+  const int nvec = cols / VN;
+  float mean = 0.f;
+  if (kLayerNorm) {
+    float s = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      Vec<T> t;
+      t.load(srow + i * VN);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) s += t.v[j];
+    }
+    mean = warp_sum(s) / cols;
+  }
+  float q = 0.f;
+  for (int i = lane; i < nvec; i += 32) {
+    Vec<T> t;
+    t.load(srow + i * VN);
+#pragma unroll
+    for (int j = 0; j < VN; ++j) {
+      const float d = t.v[j] - mean;
+      q += d * d;
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / cols + eps);
+  if (!kLayerNorm && rstd_out != nullptr && lane == 0) rstd_out[row] = rstd;
+  T* yr = y + row * y_ld;
+  if (kLayerNorm) {
+    const int64_t b = row / rows_per_batch;
+    const T* sc = scale + b * mod_stride;
+    const T* sh = shift + b * mod_stride;
+    for (int i = lane; i < nvec; i += 32) {
+      Vec<T> t, a, d;
+      t.load(srow + i * VN);
+      a.load_nc(sc + i * VN);
+      d.load_nc(sh + i * VN);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) t.v[j] = (t.v[j] - mean) * rstd * (1.0f + a.v[j]) + d.v[j];
+      t.store(yr + i * VN);
+    }
+  } else {
+    for (int i = lane; i < nvec; i += 32) {
+      Vec<T> t, wv;
+      t.load(srow + i * VN);
+      wv.load_nc(scale + i * VN);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) t.v[j] = t.v[j] * rstd * wv.v[j];
+      t.store(yr + i * VN);
+    }
+  }
+}
+
+// True when the bulk-copy kernel applies: rows of 2-24 KB, 16-byte multiples, 16-byte aligned.
+static inline bool bulk_rows_ok(int64_t cols, size_t elt, const RowAddr& a) {
+  const int64_t row_bytes = cols * (int64_t)elt;
+  if (row_bytes < 2048 || row_bytes > 24576 || row_bytes % 16) return false;
+  return (a.s0 * (int64_t)elt) % 16 == 0 && (a.s1 * (int64_t)elt) % 16 == 0 && (a.s2 * (int64_t)elt) % 16 == 0;
+}
+
+template <typename T, bool kLayerNorm>
+static void launch_norm_bulk(const T* x, const T* scale, const T* shift, T* y, float* rstd, int64_t rows,
+                             int64_t cols, int64_t rpb, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps,
+                             cudaStream_t st) {
+  const size_t smem = 128 + 8 * (size_t)cols * sizeof(T);
+  auto kern = norm_rows_bulk_kernel<T, kLayerNorm>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  kern<<<(unsigned)((rows + 7) / 8), 256, smem, st>>>(x, scale, shift, y, rstd, rows, (int)cols, rpb, xaddr, y_ld,
+                                                       mod_stride, eps);
+}
+
 template <typename T>
 static int launch_ln_mod(const void* x, const void* scale, const void* shift, void* y, int64_t rows,
                          int64_t cols, int64_t rpb, int64_t x_ld, int64_t y_ld, int64_t mod_stride,
@@ -197,6 +321,13 @@ static int launch_ln_mod(const void* x, const void* scale, const void* shift, vo
   const T* sh = static_cast<const T*>(shift);
   T* yp = static_cast<T*>(y);
   const int64_t vecs = cols / VN;
+  {
+    RowAddr xaddr{1, rows > 0 ? rows : 1, 0, 0, x_ld};
+    if (bulk_rows_ok(cols, sizeof(T), xaddr) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+      launch_norm_bulk<T, true>(xp, sc, sh, yp, nullptr, rows, cols, rpb, xaddr, y_ld, mod_stride, eps, st);
+      return FLUXB_OK;
+    }
+  }
 #define FLUXB_LN_CASE(G, VPL)                                                                  \
   if (vecs == (G) * (VPL)) {                                                                   \
     const int64_t gpb = 256 / (G);                                                             \
@@ -216,14 +347,6 @@ static int launch_ln_mod(const void* x, const void* scale, const void* shift, vo
 // ----------------------------------------------------------------------------------------
 // RMSNorm forward.  Input rows addressed through a 3-level stride (head-split views).
 // ----------------------------------------------------------------------------------------
-struct RowAddr {
-  int64_t n1, n2, s0, s1, s2;
-  __device__ __forceinline__ int64_t offset(int64_t row) const {
-    const int64_t i2 = row % n2;
-    const int64_t t = row / n2;
-    return (t / n1) * s0 + (t % n1) * s1 + i2 * s2;
-  }
-};
 
 template <typename T, int G, int VPL>
 __global__ void __launch_bounds__(256, (VPL <= 12 ? 3 : (VPL <= 24 ? 2 : 1)))
@@ -300,6 +423,10 @@ static int launch_rms(const void* x, const void* w, void* y, float* rstd, int64_
   const T* wp = static_cast<const T*>(w);
   T* yp = static_cast<T*>(y);
   const int64_t vecs = cols / VN;
+  if (bulk_rows_ok(cols, sizeof(T), addr) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    launch_norm_bulk<T, false>(xp, wp, nullptr, yp, rstd, rows, cols, 1, addr, cols, 0, eps, st);
+    return FLUXB_OK;
+  }
 #define FLUXB_RMS_CASE(G, VPL)                                                                 \
   if (vecs == (G) * (VPL)) {                                                                   \
     const int64_t gpb = 256 / (G);                                                             \
