@@ -195,13 +195,15 @@ class SingleStreamBlock(nn.Module):
         self.modulation = Modulation(hidden_size, double=False)
         self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
 
-    def forward(self, x: Tensor, vec: Tensor, pe: Tensor) -> Tensor:
+    def forward(self, x: Tensor, vec: Tensor, pe: Tensor, modulation: Tensor | None = None) -> Tensor:
+        """`modulation` may carry the packed [B, 3C] output of `self.modulation.packed(vec)`
+        computed ahead of time (it depends on `vec` only); by default it is computed here."""
         _check_inputs(x, vec)
         x = x.contiguous()
         B, L, C = x.shape
         H, M = self.num_heads, self.mlp_hidden_dim
         D = C // H
-        mod = self.modulation.packed(vec)  # [B, 3C] = shift | scale | gate
+        mod = modulation if modulation is not None else self.modulation.packed(vec)  # [B, 3C] = shift | scale | gate
         x_mod = _ln_mod(x, mod, 0)
 
         # linear1: columns [0, 3C) -> qkv, columns [3C, 3C+M) -> GELU -> cat[:, :, C:]
@@ -241,7 +243,10 @@ class DoubleStreamBlock(nn.Module):
         self.txt_mlp = MLP(hidden_size, mlp_hidden_dim)
         self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
 
-    def forward(self, img: Tensor, txt: Tensor, vec: Tensor, pe: Tensor) -> tuple[Tensor, Tensor]:
+    def forward(self, img: Tensor, txt: Tensor, vec: Tensor, pe: Tensor,
+                modulation: tuple[Tensor, Tensor] | None = None) -> tuple[Tensor, Tensor]:
+        """`modulation` may carry (txt, img) packed [B, 6C] modulation tensors computed ahead of
+        time from `vec`; by default they are computed here."""
         _check_inputs(img, txt, vec)
         img, txt = img.contiguous(), txt.contiguous()
         B, Li, C = img.shape
@@ -252,7 +257,7 @@ class DoubleStreamBlock(nn.Module):
         # stream order everywhere below: (txt, img), the order of the joint sequence
         xs = (txt, img)
         Ls = (Lt, Li)
-        mods = (self.txt_mod.packed(vec), self.img_mod.packed(vec))  # [B, 6C] each
+        mods = modulation if modulation is not None else (self.txt_mod.packed(vec), self.img_mod.packed(vec))  # [B, 6C] each
         attns = (self.txt_attn, self.img_attn)
         mlps = (self.txt_mlp, self.img_mlp)
 
