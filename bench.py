@@ -461,6 +461,76 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------
+# Sequence-length sweeps with the shapes of the reference's own benchmark scripts
+# (benchmarks/{linear,attention,layer_norm,rms_norm,rope}.py: batch 4, 24 heads x 128,
+# hidden 3072; seq_len 256..4096 step 256, linear 64..2048 step 64; fp32 inputs for the norm
+# and RoPE kernels, bf16 for linear and attention), through the public operator API.  Each
+# line carries the reference's figure of merit, "GB/s" = 2 * numel(x) * element_size / time
+# (for every kernel, also the GEMM and attention), and the real work rate of the kernel.
+# Timing like triton.testing.do_bench: L2 flushed before every call, median of the calls.
+# --------------------------------------------------------------------------------------
+def run_sweep(which: str, reps: int):
+    import triton_kernels_b200 as tk
+    from triton_kernels_b200 import _lib
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    B, Hh, D, E = 4, H, C // H, C
+
+    def randn(*shape, dtype=torch.float32):
+        return torch.randn(*shape, device=dev, generator=g).to(dtype)
+
+    def median_ms(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(max(reps, 5)):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    def emit(kernel, seq, ms, x, work, unit):
+        print(json.dumps({"sweep": kernel, "batch": B, "seq_len": seq, "ms": ms,
+                          "reference_gbps": 2 * x.numel() * x.element_size() / ms * 1e-6,
+                          "work_rate": work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9), "unit": unit}), flush=True)
+
+    seqs = [256 * i for i in range(1, 17)]
+    if which in ("all", "linear"):
+        w, b = randn(E, E, dtype=torch.bfloat16), randn(E, dtype=torch.bfloat16)
+        for seq in [64 * i for i in range(1, 33)]:
+            x = randn(B, seq, E, dtype=torch.bfloat16)
+            emit("linear", seq, median_ms(lambda: tk.linear(x, w, b)), x, 2.0 * B * seq * E * E, "TFLOP/s")
+    if which in ("all", "attention"):
+        for seq in seqs:
+            q, k, v = (randn(B, Hh, seq, D, dtype=torch.bfloat16) for _ in range(3))
+            emit("attention", seq, median_ms(lambda: tk.scaled_dot_product_attention(q, k, v)), q,
+                 4.0 * B * Hh * seq * seq * D, "TFLOP/s")
+    if which in ("all", "layer_norm"):
+        for seq in seqs:
+            x, sc, sh = randn(B, seq, E), randn(B, 1, E), randn(B, 1, E)
+            emit("layer_norm_modulation", seq, median_ms(lambda: tk.layer_norm_modulation(x, sc, sh)), x,
+                 2.0 * x.numel() * 4, "GB/s")
+    if which in ("all", "rms_norm"):
+        for seq in seqs:
+            x, sc = randn(B, Hh, seq, D), randn(D)
+            emit("rms_norm", seq, median_ms(lambda: tk.rms_norm(x, sc)), x, 2.0 * x.numel() * 4, "GB/s")
+    if which in ("all", "rope"):
+        for seq in seqs:
+            q, k, pe = randn(B, Hh, seq, D), randn(B, Hh, seq, D), randn(1, 1, seq, D // 2, 2, 2)
+            emit("rope", seq, median_ms(lambda: tk.apply_rope(q, k, pe)), q, 4.0 * q.numel() * 4 + pe.numel() * 4, "GB/s")
+    code, where = _lib.device_status()
+    if code != 0:
+        raise SystemExit(f"device status word reports error {code} at {where}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -472,6 +542,8 @@ def main():
     ap.add_argument("--parallel", default="dp", choices=["dp", "ulysses"],
                     help="multi-GPU sharding: batch data-parallel (default, weak scaling) or Ulysses sequence parallelism "
                          "on a 16384+512-token block (strong scaling)")
+    ap.add_argument("--sweep", default=None, help="sequence-length sweep with the reference benchmark scripts' shapes: "
+                    "all | linear | attention | layer_norm | rms_norm | rope (--steps = timed calls per point)")
     ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")
     ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | layer_norm_modulation | rms_norm | "
                     "rope | qkv_prepare | modulation_projection | linear_gelu | attention")
@@ -481,6 +553,9 @@ def main():
         return
     if args.dit:
         run_dit(args.steps, args.warmup)
+        return
+    if args.sweep:
+        run_sweep(args.sweep, args.steps)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
