@@ -74,8 +74,13 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int tiles
 }
 
 // Applies the epilogue to 32 consecutive columns of one output row held in registers.
+// With `stage_row` == nullptr the 8-column pieces go straight to global memory with 16-byte
+// stores.  Otherwise they go to this row's 128-byte line of a shared-memory staging tile in the
+// 128-byte-swizzle layout (16-byte piece q of row r sits at ((q ^ (r & 7)) * 16), from where a
+// TMA store writes full lines; `piece0` is the index of the first piece within the line.
 __device__ __forceinline__ void epilogue_chunk(const Params& p, const uint32_t (&acc)[32], int row,
-                                               int col0, bool second) {
+                                               int col0, bool second, uint8_t* stage_row = nullptr,
+                                               int piece0 = 0, int swz = 0) {
   const int epi = second ? p.epi2 : p.epi;
   __nv_bfloat16* out = second ? p.y2 : p.y;
   const int64_t ld = second ? p.ldy2 : p.ldy;
@@ -111,10 +116,12 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, const uint32_t (
         v[6] = bf16_lo(rv.w) + bf16_lo(gv.w) * v[6]; v[7] = bf16_hi(rv.w) + bf16_hi(gv.w) * v[7];
       }
     }
-    if (row_ok) {
-      uint4 o;
-      o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
-      o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+    uint4 o;
+    o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
+    o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+    if (stage_row != nullptr) {
+      *reinterpret_cast<uint4*>(stage_row + (((piece0 + j) ^ swz) << 4)) = o;  // rows/cols past the edge are clipped by the TMA store
+    } else if (row_ok) {
       *reinterpret_cast<uint4*>(out + (int64_t)row * ld + out_col0 + j * 8) = o;
     }
   }
@@ -270,13 +277,15 @@ constexpr int BM = 128;       // rows of x per CTA (256 per pair)
 constexpr int BN = 256;       // output columns per tile
 constexpr int BNH = 128;      // rows of w loaded by each CTA
 constexpr int BK = 64;
-constexpr int STAGES = 6;
+constexpr int STAGES = 5;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int OUT_CHUNK_COLS = 64;                       // output columns per staged TMA store
+constexpr int OUT_BUF_BYTES = BM * OUT_CHUNK_COLS * 2;   // 128 rows x 128 bytes
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BUF_BYTES + 1024 + 256;
 constexpr int MAX_PROBLEMS = 4;
 
 // Up to four GEMMs that differ in operands, outputs and row counts run as ONE persistent
@@ -285,6 +294,7 @@ constexpr int MAX_PROBLEMS = 4;
 // its own; riding along with the image stream's GEMM it fills the tail of that launch instead.
 struct Problem {
   CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_y, tm_y2;  // outputs (columns below / from `split`), box 64 columns x 128 rows
   Params p;
   int tile_start;  // index of this problem's first tile in the concatenated order
   int tiles_m;     // 256-row blocks
@@ -309,7 +319,8 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* out_stage = smem + STAGES * STAGE_BYTES;  // two 16 KB output staging tiles
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(out_stage + 2 * OUT_BUF_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -339,6 +350,8 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
     for (int i = 0; i < g.count; ++i) {
       tma_prefetch_desc(&g.prob[i].tm_a);
       tma_prefetch_desc(&g.prob[i].tm_b);
+      tma_prefetch_desc(&g.prob[i].tm_y);
+      tma_prefetch_desc(&g.prob[i].tm_y2);
     }
   }
   if (warp == 1) {
@@ -411,6 +424,8 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
     int local = 0;
     bool ok = true;
     const uint32_t acc_empty_leader0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+    const bool store_issuer = warp == 2 && lane == 0;
+    uint32_t out_chunks = 0;
     for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
       const Problem& pr = g.prob[find_problem(g, tile)];
       const Params& p = pr.p;
@@ -420,22 +435,47 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, status, 45)) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = m_blk * 2 * BM + (int)rank * BM + quad * 32 + lane;
+      const int row0 = m_blk * 2 * BM + (int)rank * BM;
+      const int r_local = quad * 32 + lane;
+      const int row = row0 + r_local;
       const int n0 = n_blk * BN;
       const bool second = n0 >= p.split;
+      const CUtensorMap* tm_out = second ? &pr.tm_y2 : &pr.tm_y;
+      const int out_col0 = second ? n0 - p.split : n0;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      // The tile leaves in four 64-column pieces: registers -> swizzled staging tile in shared
+      // memory -> one TMA store of full 128-byte lines.  (Storing 16 bytes per thread straight
+      // to global memory, 32 different rows per warp instruction, cost 9 % of the GEMM.)
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        if (n0 + c * 32 >= p.N) break;
-        uint32_t r[32];
-        tmem_ld_x32(t_addr + c * 32, r);
+      for (int c = 0; c < BN / OUT_CHUNK_COLS; ++c) {
+        if (n0 + c * OUT_CHUNK_COLS >= p.N) break;  // uniform
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS, r0);
+        tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS + 32, r1);
         tmem_wait_ld();
-        epilogue_chunk(p, r, row, n0 + c * 32, second);
+        uint8_t* buf = out_stage + (out_chunks & 1) * OUT_BUF_BYTES;
+        // the store issued from this staging tile two pieces ago must have read it out
+        if (store_issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint8_t* line = buf + r_local * 128;
+        epilogue_chunk(p, r0, row, n0 + c * OUT_CHUNK_COLS, second, line, 0, r_local & 7);
+        epilogue_chunk(p, r1, row, n0 + c * OUT_CHUNK_COLS + 32, second, line, 4, r_local & 7);
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (store_issuer) {
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                           reinterpret_cast<uint64_t>(tm_out)),
+                       "r"(smem_u32(buf)), "r"(out_col0 + c * OUT_CHUNK_COLS), "r"(row0)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        ++out_chunks;
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader0 + acc * 8);
     }
+    if (store_issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // staging tiles outlive their stores
   }
 
   tc_fence_before_sync();
@@ -574,6 +614,24 @@ extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int co
       const int grid = pr.p.num_tiles < sm_count() ? pr.p.num_tiles : sm_count();
       gemm_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(pr.tm_a, pr.tm_b, pr.p);
       continue;
+    }
+    {
+      const fluxb_linear_problem& a = problems[i];
+      const int64_t n_first = split < N ? split : N;
+      const uint32_t box[2] = {fluxb::gemm2::OUT_CHUNK_COLS, fluxb::gemm2::BM};
+      const uint64_t dims[2] = {(uint64_t)n_first, (uint64_t)a.M};
+      const uint64_t strides[1] = {(uint64_t)a.ldy * 2};
+      rc = n_first > 0 ? encode_tmap_bf16(&pr.tm_y, a.y, 2, dims, strides, box) : FLUXB_OK;
+      if (rc != FLUXB_OK) return rc;
+      if (split < N) {
+        const uint64_t dims2[2] = {(uint64_t)(N - split), (uint64_t)a.M};
+        const uint64_t strides2[1] = {(uint64_t)a.ldy2 * 2};
+        rc = encode_tmap_bf16(&pr.tm_y2, a.y2, 2, dims2, strides2, box);
+        if (rc != FLUXB_OK) return rc;
+        if (n_first == 0) pr.tm_y = pr.tm_y2;
+      } else {
+        pr.tm_y2 = pr.tm_y;
+      }
     }
     pr.tiles_m = (int)((problems[i].M + 255) / 256);
     pr.tile_start = g.total_tiles;
