@@ -140,7 +140,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 128);
+      mbar_init(&p_full[t], 4);  // one arrival per softmax warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -336,7 +336,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       l += (sums[0].x + sums[0].y) + (sums[1].x + sums[1].y);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(&p_full[t]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);  // 4 arrivals per tile instead of 128 serialised ones
     }
 
     if (ok && mbar_wait(&s_full[t], n_kv & 1, abort_flag, p.status, 32)) {
