@@ -100,11 +100,11 @@ int fluxb_modulation_gemv(const void* vec, const void* w, const void* bias, void
                           int64_t N, int64_t K, int apply_silu, fluxb_stream_t stream);
 
 /*
- * Non-causal attention softmax(q k^T * sm_scale) v, bf16, head_dim 128.
+ * Non-causal attention softmax(q k^T * sm_scale) v, bf16, head_dim 64 or 128.
  * Replaces triton_kernels/kernels/attention.py:173-221 (`scaled_dot_product_attention`,
  * kernels `_attn_fwd` :69-170 / `_attn_fwd_inner` :10-46).
- *   q,k,v: [B,H,L,128] addressed through element strides (batch, head, row); last dim contiguous.
- *   o: same addressing with its own strides, so the caller can ask for [B,L,H*128] directly
+ *   q,k,v: [B,H,L,D] addressed through element strides (batch, head, row); last dim contiguous.
+ *   o: same addressing with its own strides, so the caller can ask for [B,L,H*D] directly
  *   (the rearrange at triton_kernels/modules/blocks.py:14) or write into a wider buffer.
  *   Any Lq, Lk >= 1 (tails masked).  Strides must be multiples of 8 elements.
  */

@@ -55,7 +55,7 @@ def test_argument_validation_needs_no_gpu(lib):
     """Bad arguments are rejected on the host before anything is launched."""
     from triton_kernels_b200 import _lib
 
-    rc = lib.fluxb_attention(None, None, None, None, 1, 1, 128, 128, 64, *([128] * 12), 1.0, None)
+    rc = lib.fluxb_attention(None, None, None, None, 1, 1, 128, 128, 32, *([128] * 12), 1.0, None)
     assert rc == _lib.ERR_UNSUPPORTED and b"head_dim" in lib.fluxb_last_error()
     rc = lib.fluxb_linear(None, None, None, None, 128, 256, 64, 64, 64, 256, 0, None, 0, 256, 0, None, 0, None, 0, 1, 0, None)
     assert rc == _lib.ERR_BAD_ARG

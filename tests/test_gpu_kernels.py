@@ -289,6 +289,34 @@ def test_attention(tk, B, H, L):
     assert rel_l2(o, want) < 1e-2
 
 
+@pytest.mark.parametrize("B,H,L", [(2, 4, 256), (1, 8, 512), (4, 2, 1024), (1, 24, 300), (1, 3, 65)])
+def test_attention_head_dim_64(tk, B, H, L):
+    """The reference's attention test also sweeps head_dim 64 (tests/test_attention.py:9)."""
+    g = gen(27)
+    q, k, v = (torch.randn(B, H, L, 64, generator=g).to(BF) for _ in range(3))
+    o = tk.scaled_dot_product_attention(q.cuda(), k.cuda(), v.cuda())
+    want = O.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    torch.testing.assert_close(o.float().cpu(), want, atol=1e-2, rtol=2e-2)
+    assert rel_l2(o, want) < 1e-2
+
+
+@pytest.mark.parametrize("B,L,K,N", [(1, 256, 256, 1024), (2, 512, 512, 2048), (4, 1024, 1024, 3072), (4, 256, 1024, 2048)])
+@pytest.mark.parametrize("act", ["", "GELU"])
+def test_linear_reference_grid(tk, B, L, K, N, act):
+    """Corners of the reference's own grid (tests/test_linear.py:7-12): batched [B, L, K] inputs
+    and, like there, N(0,1) weights; its tolerances are 1e-5 / 0.02 absolute against a bf16
+    F.linear, here the comparison is against float64 with the bf16 tolerance."""
+    g = gen(28)
+    x = torch.randn(B, L, K, generator=g).to(BF)
+    w = torch.randn(N, K, generator=g).to(BF)
+    b = torch.randn(N, generator=g).to(BF)
+    y = tk.linear(x.cuda(), w.cuda(), b.cuda(), activation=act)
+    want = O.linear(x.double(), w.double(), b.double(), act)
+    assert y.shape == (B, L, N)
+    assert rel_l2(y, want) < 4e-3
+    torch.testing.assert_close(y.float().cpu(), want.float(), atol=0.02 * K**0.5, rtol=2e-2)
+
+
 def test_attention_sharp_softmax_and_custom_scale(tk):
     """Large logits make the running maximum jump, exercising the lazy-rescale path."""
     g = gen(18)

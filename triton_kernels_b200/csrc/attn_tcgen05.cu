@@ -19,15 +19,15 @@
 namespace fluxb {
 namespace attn {
 
-constexpr int D = 128;
+// kD (kernel template parameter): head_dim, 64 or 128.
 constexpr int BQ = 128;             // rows per query tile
 constexpr int BKV = 128;            // keys per tile
 constexpr int HALF_BYTES = 128 * 128;  // [128 rows][64 bf16] swizzled block
-constexpr int TILE_BYTES = 2 * HALF_BYTES;
+__host__ __device__ constexpr int tile_bytes(int d) { return (d / 64) * HALF_BYTES; }  // one Q, K or V tile: 128 rows x d
 constexpr int KV_SLOTS = 4;
 constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_SLOTS * TILE_BYTES + 1024 + 256;
+__host__ __device__ constexpr int smem_bytes(int d) { return 2 * tile_bytes(d) + KV_SLOTS * tile_bytes(d) + 1024 + 256; }
 constexpr float kRescaleThreshold = 8.0f;
 // kPolyEvery (kernel template parameter): every n-th pair of a row takes the polynomial exp2; 1000 = none.
 
@@ -108,10 +108,12 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
       : "memory");
 }
 
-template <int kPolyEvery>
+template <int kPolyEvery, int kD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const Params p) {
+  constexpr int D = kD;
+  constexpr int TILE_BYTES = tile_bytes(kD);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -162,7 +164,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * TILE_BYTES);
       for (int t = 0; t < 2; ++t)
-        for (int hf = 0; hf < 2; ++hf)
+        for (int hf = 0; hf < D / 64; ++hf)
           tma_load_4d(q_smem + t * TILE_BYTES + hf * HALF_BYTES, &tm_q, q_full, hf * 64, q0 + t * BQ,
                       head, batch);
       bool ok = true;
@@ -174,8 +176,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         mbar_expect_tx(&kv_full[slot], TILE_BYTES);
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
         const int row0 = (i >> 1) * BKV;
-        tma_load_4d(dst, tm, &kv_full[slot], 0, row0, head, batch);
-        tma_load_4d(dst + HALF_BYTES, tm, &kv_full[slot], 64, row0, head, batch);
+        for (int hf = 0; hf < D / 64; ++hf)
+          tma_load_4d(dst + hf * HALF_BYTES, tm, &kv_full[slot], hf * 64, row0, head, batch);
       }
     }
     __syncwarp();
@@ -301,7 +303,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         l *= alpha;
         m_used = m_new;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
           tmem_ld_x32(o_addr + c * 32, o);
           tmem_wait_ld();
@@ -345,7 +347,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + (int64_t)row * p.o_sl;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         tmem_ld_x32(o_addr + c * 32, o);
         tmem_wait_ld();
@@ -377,12 +379,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
 using namespace fluxb;
 
-static int encode_qkv_map(CUtensorMap* tm, const void* base, int64_t B, int64_t H, int64_t L,
+static int encode_qkv_map(CUtensorMap* tm, const void* base, int64_t B, int64_t H, int64_t L, int64_t D,
                           int64_t sb, int64_t sh, int64_t sl) {
   // A size-1 dimension may come with any stride; give the encoder a harmless valid one.
   if (H == 1 || sh == 0) sh = sl * L;
   if (B == 1 || sb == 0) sb = sh * H;
-  const uint64_t dims[4] = {128, (uint64_t)L, (uint64_t)H, (uint64_t)B};
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)L, (uint64_t)H, (uint64_t)B};
   const uint64_t strides[3] = {(uint64_t)sl * 2, (uint64_t)sh * 2, (uint64_t)sb * 2};
   const uint32_t box[4] = {64, 128, 1, 1};
   return encode_tmap_bf16(tm, base, 4, dims, strides, box);
@@ -400,7 +402,8 @@ extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void
                                int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
                                int64_t o_sl, float sm_scale, fluxb_stream_t stream) {
   using namespace fluxb::attn;
-  if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "attention: head_dim %lld (only 128)", (long long)D);
+  if (D != 128 && D != 64)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "attention: head_dim %lld (64 and 128 are built)", (long long)D);
   if (B < 0 || H < 0 || Lq < 0 || Lk < 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: negative size");
   if (B == 0 || H == 0 || Lq == 0) return FLUXB_OK;
   if (Lk == 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: no keys");
@@ -410,16 +413,16 @@ extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void
   const int64_t strides[] = {q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, v_sb, v_sh, v_sl, o_sb, o_sh, o_sl};
   for (int64_t s : strides)
     if (s % 8 || s < 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: strides must be non-negative multiples of 8 elements");
-  if (q_sl < 128 || k_sl < 128 || v_sl < 128 || o_sl < 128)
+  if (q_sl < D || k_sl < D || v_sl < D || o_sl < D)
     return set_error(FLUXB_ERR_BAD_ARG, "attention: row stride below head_dim");
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(o)) & 15)
     return set_error(FLUXB_ERR_BAD_ARG, "attention: pointers must be 16-byte aligned");
 
   CUtensorMap tm_q, tm_k, tm_v;
-  int rc = encode_qkv_map(&tm_q, q, B, H, Lq, q_sb, q_sh, q_sl);
-  if (rc == FLUXB_OK) rc = encode_qkv_map(&tm_k, k, B, H, Lk, k_sb, k_sh, k_sl);
-  if (rc == FLUXB_OK) rc = encode_qkv_map(&tm_v, v, B, H, Lk, v_sb, v_sh, v_sl);
+  int rc = encode_qkv_map(&tm_q, q, B, H, Lq, D, q_sb, q_sh, q_sl);
+  if (rc == FLUXB_OK) rc = encode_qkv_map(&tm_k, k, B, H, Lk, D, k_sb, k_sh, k_sl);
+  if (rc == FLUXB_OK) rc = encode_qkv_map(&tm_v, v, B, H, Lk, D, v_sb, v_sh, v_sl);
   if (rc != FLUXB_OK) return rc;
 
   Params p;
@@ -433,16 +436,19 @@ extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void
   p.v_sbo = env_u32("FLUXB_ATTN_V_SBO", 1024);
   p.status = device_status_ptr();
 
+  // Every fourth pair of a row takes the polynomial exp2 unless FLUXB_ATTN_POLY=0 (all on MUFU).
   static const int poly_env = (int)env_u32("FLUXB_ATTN_POLY", 4);
-  auto kern = attn_kernel<4>;
-  if (poly_env == 0) kern = attn_kernel<1000>;
-  else if (poly_env == 2) kern = attn_kernel<2>;
-  else if (poly_env == 3) kern = attn_kernel<3>;
-  else if (poly_env == 8) kern = attn_kernel<8>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  auto kern = attn_kernel<4, 128>;
+  if (D == 128) {
+    if (poly_env == 0) kern = attn_kernel<1000, 128>;
+  } else {
+    kern = poly_env == 0 ? attn_kernel<1000, 64> : attn_kernel<4, 64>;
+  }
+  const int smem = smem_bytes((int)D);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: cannot set shared memory size: %s", cudaGetErrorString(e));
   dim3 grid((unsigned)((Lq + 2 * BQ - 1) / (2 * BQ)), (unsigned)H, (unsigned)B);
-  kern<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, p);
+  kern<<<grid, THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;

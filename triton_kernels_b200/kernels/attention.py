@@ -40,8 +40,8 @@ def scaled_dot_product_attention(
     _lib.require_cuda(q, k, v)
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise NotImplementedError("attention runs in bfloat16 only (the reference casts P to bf16 as well)")
-    if HEAD_DIM_K != 128:
-        raise NotImplementedError(f"attention is built for head_dim 128 (Flux); got {HEAD_DIM_K}")
+    if HEAD_DIM_K not in (64, 128):
+        raise NotImplementedError(f"attention is built for head_dim 64 and 128 (Flux uses 128); got {HEAD_DIM_K}")
 
     def usable(t):
         return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
