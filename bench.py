@@ -11,7 +11,7 @@ the data path, weak scaling.  Rank 0 prints one JSON line.
   value     tokens/s with inputs resident in HBM (CUDA events, max over ranks)
   e2e       tokens/s through the public module call with HOST inputs/outputs: pinned-host ->
             device copies of img/txt/vec and a device -> host copy of both outputs every step,
-            pipelined over three streams
+            pipelined over three streams (the module call is a CUDA-graph replay here too)
   roofline  the largest GEMM launch of the step (MLP up-projection of both streams, grouped:
             M=512+4096, K=3072, N=12288, GELU epilogue) timed per launch with CUDA events inside real steps,
             against the measured bf16 peak in MEASURED_PEAKS.json
@@ -648,6 +648,9 @@ def main():
         dom_ms = sum(durs) / len(durs)
 
         # ------------------------------------------------------------ end to end with host buffers
+        # Two captured copies of the module call, each with its own device-side input and output
+        # buffers, so that step i+1's host->device copy and step i-1's device->host copy run
+        # under step i's kernels.  (--no-graph: eager module calls on fresh tensors instead.)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         s_cmp = torch.cuda.current_stream()
         bufs = [[torch.empty_like(img_d), torch.empty_like(txt_d), torch.empty_like(vec_d)] for _ in range(2)]
@@ -655,6 +658,16 @@ def main():
         in_ready = [torch.cuda.Event() for _ in range(2)]
         in_free = [torch.cuda.Event() for _ in range(2)]
         out_ready = [torch.cuda.Event() for _ in range(2)]
+        out_free = [torch.cuda.Event() for _ in range(2)]
+        graphs = None
+        if not args.no_graph:
+            graphs = []
+            for b in range(2):
+                for dst, src in zip(bufs[b], (img_d, txt_d, vec_d)):
+                    dst.copy_(src)
+                gf = GraphedForward(lambda i, t, v: block(i, t, v, pe_d), tuple(bufs[b]))
+                bufs[b] = list(gf.static_inputs)  # the copies land directly in the captured inputs
+                graphs.append(gf)
 
         def e2e_steps(n):
             keep = []
@@ -666,20 +679,29 @@ def main():
                         dst.copy_(src, non_blocking=True)
                     in_ready[b].record(s_in)
                 s_cmp.wait_event(in_ready[b])
-                oi, ot = block(bufs[b][0], bufs[b][1], bufs[b][2], pe_d)
+                if graphs is not None:
+                    s_cmp.wait_event(out_free[b])  # this graph's output buffers were read out
+                    graphs[b].graph.replay()
+                    oi, ot = graphs[b].static_outputs
+                else:
+                    oi, ot = block(bufs[b][0], bufs[b][1], bufs[b][2], pe_d)
                 in_free[b].record(s_cmp)
                 out_ready[b].record(s_cmp)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(out_ready[b])
                     outs_h[b][0].copy_(oi, non_blocking=True)
                     outs_h[b][1].copy_(ot, non_blocking=True)
-                    oi.record_stream(s_out)
-                    ot.record_stream(s_out)
+                    out_free[b].record(s_out)
+                    if graphs is None:
+                        oi.record_stream(s_out)
+                        ot.record_stream(s_out)
                 keep.append((oi, ot))
                 if len(keep) > 2:
                     keep.pop(0)
             s_cmp.wait_stream(s_out)
 
+        for ev in out_free:
+            ev.record(s_cmp)
         for ev in in_free:
             ev.record(s_cmp)
         e2e_steps(args.warmup)
@@ -697,11 +719,15 @@ def main():
     if code != 0:
         raise SystemExit(f"device status word reports error {code} at {where}")
 
+    # The GEMM is timed inside back-to-back block steps, where the SM clock has already dropped
+    # under load: the sustained cuBLAS figure is the matching denominator; the burst figure is
+    # reported beside it.
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     if peaks_path.exists():
-        peak, peak_src = json.loads(peaks_path.read_text())["bf16_tflops"], "measured (burst)"
+        pk = json.loads(peaks_path.read_text())
+        peak, peak_burst, peak_src = pk["bf16_tflops_sustained"], pk["bf16_tflops"], "measured (sustained)"
     else:
-        peak, peak_src = 1590.0, "fallback"
+        peak, peak_burst, peak_src = 1400.0, 1590.0, "fallback"
     dom_flop = 2.0 * DOM_M * DOM_N * DOM_K
     achieved = dom_flop / (dom_ms * 1e-3) / 1e12
 
@@ -729,7 +755,8 @@ def main():
             "roofline": {
                 "bound": "tensor", "kernel": f"gemm_pair_kernel, grouped MLP-up M={L_TXT}+{L_IMG} K={DOM_K} N={DOM_N} +bias+GELU",
                 "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "TFLOP/s",
-                "frac": achieved / peak, "launch_ms": dom_ms, "traffic": NCU_TRAFFIC_BYTES,
+                "frac": achieved / peak, "peak_burst": peak_burst, "frac_of_burst": achieved / peak_burst,
+                "launch_ms": dom_ms, "traffic": NCU_TRAFFIC_BYTES,
             },
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -242,6 +242,7 @@ class DoubleStreamBlock(nn.Module):
         self.txt_attn = SelfAttention(dim=hidden_size, num_heads=num_heads, qkv_bias=qkv_bias)
         self.txt_mlp = MLP(hidden_size, mlp_hidden_dim)
         self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
+        self._side_stream = None  # created on first use
 
     def forward(self, img: Tensor, txt: Tensor, vec: Tensor, pe: Tensor,
                 modulation: tuple[Tensor, Tensor] | None = None) -> tuple[Tensor, Tensor]:
@@ -257,16 +258,32 @@ class DoubleStreamBlock(nn.Module):
         # stream order everywhere below: (txt, img), the order of the joint sequence
         xs = (txt, img)
         Ls = (Lt, Li)
-        mods = modulation if modulation is not None else (self.txt_mod.packed(vec), self.img_mod.packed(vec))  # [B, 6C] each
         attns = (self.txt_attn, self.img_attn)
         mlps = (self.txt_mlp, self.img_mlp)
+        # The block opens with bandwidth-bound work only (two weight-streaming modulation
+        # projections, two LayerNorms); the text stream's half runs on a side stream next to the
+        # image stream's so that the two together keep HBM busy.
+        main = torch.cuda.current_stream()
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream()
+        side = self._side_stream
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            txt_mod = modulation[0] if modulation is not None else self.txt_mod.packed(vec)
+            h_txt = _ln_mod(txt, txt_mod, 0)
+        img_mod = modulation[1] if modulation is not None else self.img_mod.packed(vec)
+        h_img = _ln_mod(img, img_mod, 0)
+        main.wait_stream(side)
+        for t_ in (txt_mod, h_txt):
+            t_.record_stream(main)
+        mods = (txt_mod, img_mod)  # [B, 6C] each
 
         def gate_of(mod, chunk, b=None):
             g = mod[:, chunk * C : (chunk + 1) * C]
             return (g, g.stride(0) if B > 1 else 0) if b is None else (g[b : b + 1], 0)
 
-        # LayerNorm+modulation, then both streams' qkv projections in one launch
-        h1 = [_ln_mod(x, m, 0) for x, m in zip(xs, mods)]
+        # both streams' qkv projections in one launch
+        h1 = [h_txt, h_img]
         qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]
         linear_grouped_into([
             dict(x2d=h.view(B * L, C), w=a.qkv.weight, b=a.qkv.bias, y=o.view(B * L, 3 * C))
