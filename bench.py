@@ -54,15 +54,29 @@ NCU_TRAFFIC_BYTES = 191.2e6  # dram read+write bytes per launch of the timed GEM
 
 
 def make_inputs(seed: int, l_img: int = L_IMG, l_txt: int = L_TXT, grid: int = GRID):
-    """Seeded fp32 parameters and activations of the double-stream block config (CPU)."""
-    from oracle import flux_oracle as O
+    """Seeded fp32 parameters and activations of the double-stream block config (CPU tensors).
+
+    Parameter names, shapes and draw order are those of the block's own state-dict; weights
+    N(0, 0.02), biases 0, QK-norm scales 1, activations and vec N(0, 1).  Nothing here touches
+    the oracle: the GPU arm only needs numbers, and the CPU legs feed the same dict to it."""
+    from triton_kernels_b200.flux import EmbedND, flux_position_ids
+    from triton_kernels_b200.modules import DoubleStreamBlock
 
     g = torch.Generator().manual_seed(seed)
-    params = O.init_params(O.double_block_shapes(C, MLP_RATIO), g)
+    with torch.device("meta"):
+        shapes = {k: tuple(v.shape) for k, v in DoubleStreamBlock(C, H, MLP_RATIO).state_dict().items()}
+    params = {}
+    for name, shape in shapes.items():
+        if name.endswith(".scale"):
+            params[name] = torch.ones(shape)
+        elif name.endswith(".bias"):
+            params[name] = torch.zeros(shape)
+        else:
+            params[name] = 0.02 * torch.randn(shape, generator=g)
     img = torch.randn(1, l_img, C, generator=g)
     txt = torch.randn(1, l_txt, C, generator=g)
     vec = torch.randn(1, C, generator=g)
-    pe = O.embed_nd(O.flux_position_ids(l_txt, l_img // grid, grid), [16, 56, 56])
+    pe = EmbedND(C // H, 10000, [16, 56, 56])(flux_position_ids(l_txt, l_img // grid, grid))
     return params, img, txt, vec, pe
 
 

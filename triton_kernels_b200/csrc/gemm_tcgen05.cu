@@ -1,18 +1,24 @@
-// y = x · w^T with fused epilogues, as a persistent, warp-specialised tcgen05 kernel.
+// y = x · w^T with fused epilogues, as persistent, warp-specialised tcgen05 kernels.
 //
-//   warp 0      TMA producer: streams 128x64 tiles of x and 256x64 tiles of w (bf16, 128-byte
-//               swizzle) through a 4-stage shared-memory ring.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16) from shared
-//               memory into one of two 256-column fp32 accumulators in TMEM; tcgen05.commit
-//               releases ring slots and publishes finished accumulators.
-//   warps 2-5   epilogue: each warp reads its 32-lane TMEM quadrant with tcgen05.ld, applies
-//               bias / GELU / gate+residual in fp32 and stores bf16 rows with 16-byte stores.
-//               Because there are two accumulators the epilogue of tile i overlaps the main
-//               loop of tile i+1.
+// Two kernels share the role layout (192 threads):
+//   warp 0      TMA producer: streams 64-wide K slices of x and w (bf16, 128-byte swizzle)
+//               through a shared-memory ring.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma from shared memory into one of two
+//               256-column fp32 accumulators in TMEM; tcgen05.commit releases ring slots and
+//               publishes finished accumulators.
+//   warps 2-5   epilogue: each warp reads its 32-lane TMEM quadrant with tcgen05.ld and applies
+//               bias / GELU / gate+residual in fp32.  Because there are two accumulators the
+//               epilogue of tile i overlaps the main loop of tile i+1.
 //
-// Tiles are handed out statically (tile = blockIdx.x + i * gridDim.x) in an order that keeps
-// 8 row-blocks of x and a band of w resident in L2 at a time.  Edge tiles rely on TMA zero
-// fill for loads and on masks for stores.  Every barrier wait is bounded.
+//   gemm_pair_kernel (default)  clusters of two CTAs share a 256x256 tile through
+//               cta_group::2 MMAs; 5-stage ring of 32 KB per CTA; output leaves through
+//               swizzled staging tiles and TMA stores; up to four problems per launch.
+//   gemm_kernel (FLUXB_GEMM_PAIR=0)  one CTA per 128x256 tile, 4-stage ring of 48 KB, direct
+//               16-byte stores.
+//
+// Tiles are handed out statically (tile = id + i * stride) in an L2-aware order (tile_coords).
+// Edge tiles rely on TMA zero fill for loads and on TMA clipping / masks for stores.  Every
+// barrier wait is bounded.
 #include <stdio.h>
 #include <stdlib.h>
 
