@@ -5,7 +5,8 @@
 //   warps 0-3   softmax group 0: thread r owns query row r of tile 0
 //   warps 4-7   softmax group 1: same for tile 1
 //   warp  8     TMA producer: Q once, then K_j, V_j through a 4-slot ring of 32 KB tiles
-//   warp  9     MMA issuer (one thread): S_t = Q_t K_j^T and O_t += P_t V_j
+//   warp  9     MMA issuer (whole warp walks the loop, one elected lane issues): S_t = Q_t K_j^T and
+//               O_t += P_t V_j
 // TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  P_t (bf16) is written back
 // over the first 64 columns of S_t by the softmax threads and fed to the second MMA straight
 // from TMEM, so probabilities never touch shared memory.  While group 0 does softmax on S_0 the
@@ -183,7 +184,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     __syncwarp();
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (waits, address arithmetic) and one elected lane issues each
+    // MMA and commit: control flow and descriptor words stay warp-uniform, which keeps the
+    // per-instruction overhead of the issuing thread well below the 64 cycles an MMA lasts.
+    {
       constexpr uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, 0, 0);  // A = Q (K-major), B = K (K-major)
       constexpr uint32_t idesc_pv = make_idesc_bf16(BQ, D, 0, 1);    // A = P (TMEM), B = V (MN-major)
       const uint32_t q_addr = smem_u32(q_smem);
@@ -197,17 +201,25 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const uint32_t q_lo = (q_addr & 0x3ffffu) >> 4;
       const uint32_t kv_lo = (kv_addr & 0x3ffffu) >> 4;
 
+      auto wait = [&](uint64_t* bar, uint32_t parity, int where) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.status, where)) != 0;
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (elect_one()) umma_commit(bar);
+      };
       auto issue_qk = [&](int t, int slot) {
         const uint32_t qa = q_lo + t * (TILE_BYTES >> 4);
         const uint32_t ka = kv_lo + slot * (TILE_BYTES >> 4);
         const uint32_t d = tmem_base + t * 128;
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          // 16 elements of head_dim per step: 32 bytes inside a 128-byte row, second half-block
-          // after four steps
-          const uint32_t off = (ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2;
-          if (ks == 0) mma_ss<0>(d, qa + off, hi_kmajor, ka + off, hi_kmajor, idesc_qk);
-          else mma_ss<1>(d, qa + off, hi_kmajor, ka + off, hi_kmajor, idesc_qk);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            // 16 elements of head_dim per step: 32 bytes inside a 128-byte row, second half-block
+            // after four steps
+            const uint32_t off = (ks >> 2) * (HALF_BYTES >> 4) + (ks & 3) * 2;
+            if (ks == 0) mma_ss<0>(d, qa + off, hi_kmajor, ka + off, hi_kmajor, idesc_qk);
+            else mma_ss<1>(d, qa + off, hi_kmajor, ka + off, hi_kmajor, idesc_qk);
+          }
         }
       };
       auto issue_pv = [&](int t, int slot, bool accumulate) {
@@ -215,43 +227,45 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const uint32_t d = tmem_base + 256 + t * 128;
         const uint32_t pa = tmem_base + t * 128;
         // 16 keys per step: 16 rows of 128 bytes in each half-block; 8 TMEM columns of P.
-        if (accumulate) mma_ts<1>(d, pa, va, hi_v, idesc_pv);
-        else mma_ts<0>(d, pa, va, hi_v, idesc_pv);
+        if (elect_one()) {
+          if (accumulate) mma_ts<1>(d, pa, va, hi_v, idesc_pv);
+          else mma_ts<0>(d, pa, va, hi_v, idesc_pv);
 #pragma unroll
-        for (int ks = 1; ks < BKV / 16; ++ks) mma_ts<1>(d, pa + ks * 8, va + ks * 128, hi_v, idesc_pv);
+          for (int ks = 1; ks < BKV / 16; ++ks) mma_ts<1>(d, pa + ks * 8, va + ks * 128, hi_v, idesc_pv);
+        }
       };
 
-      ok = mbar_wait(q_full, 0, abort_flag, p.status, 21);
-      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_flag, p.status, 22);
+      ok = wait(q_full, 0, 21);
+      if (ok) ok = wait(&kv_full[0], 0, 22);
       if (ok) {
         tc_fence_after_sync();
         issue_qk(0, 0);
-        umma_commit(&s_full[0]);
+        commit(&s_full[0]);
         issue_qk(1, 0);
-        umma_commit(&s_full[1]);
-        umma_commit(&kv_empty[0]);
+        commit(&s_full[1]);
+        commit(&kv_empty[0]);
       }
       for (int j = 0; ok && j < n_kv; ++j) {
         const int iv = 2 * j + 1;
         const int v_slot = iv % KV_SLOTS;
-        if (!mbar_wait(&kv_full[v_slot], (iv / KV_SLOTS) & 1, abort_flag, p.status, 23)) { ok = false; break; }
+        if (!wait(&kv_full[v_slot], (iv / KV_SLOTS) & 1, 23)) { ok = false; break; }
         const int ik = 2 * j + 2;
         const int k_slot = ik % KV_SLOTS;
         for (int t = 0; t < 2; ++t) {
-          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status, 24)) { ok = false; break; }
+          if (!wait(&p_full[t], j & 1, 24)) { ok = false; break; }
           tc_fence_after_sync();
           issue_pv(t, v_slot, j > 0);
-          if (t == 1) umma_commit(&kv_empty[v_slot]);
+          if (t == 1) commit(&kv_empty[v_slot]);
           if (j + 1 < n_kv) {
             if (t == 0) {
-              if (!mbar_wait(&kv_full[k_slot], (ik / KV_SLOTS) & 1, abort_flag, p.status, 25)) { ok = false; break; }
+              if (!wait(&kv_full[k_slot], (ik / KV_SLOTS) & 1, 25)) { ok = false; break; }
               tc_fence_after_sync();
             }
             issue_qk(t, k_slot);
-            umma_commit(&s_full[t]);
-            if (t == 1) umma_commit(&kv_empty[k_slot]);
+            commit(&s_full[t]);
+            if (t == 1) commit(&kv_empty[k_slot]);
           } else {
-            umma_commit(&s_full[t]);  // final O_t complete
+            commit(&s_full[t]);  // final O_t complete
           }
         }
       }
