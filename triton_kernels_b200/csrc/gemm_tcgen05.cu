@@ -396,7 +396,9 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (leader && lane == 0) {
+    // The whole warp of the leader CTA walks the loop and an elected lane issues, so that
+    // addresses and descriptors stay warp-uniform.
+    if (leader) {
       constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -406,22 +408,24 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
         const int num_kb = (g.prob[find_problem(g, tile)].p.K + BK - 1) / BK;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, 43)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait_cluster(&acc_empty[acc], acc_phase ^ 1, abort_flag, status, 43))) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag, status, 44)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait_cluster(&full_bar[stage], phase, abort_flag, status, 44))) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
           const uint64_t bdesc = make_smem_desc(a_addr + A_BYTES, 16, 1024);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit_pair_both(&empty_bar[stage]);
+            for (int k = 0; k < BK / 16; ++k)
+              umma_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_pair_both(&empty_bar[stage]);
+          }
           if (++stage == g.pair_stages) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit_pair_both(&acc_full[acc]);
+        if (ok && elect_one()) umma_commit_pair_both(&acc_full[acc]);
       }
     }
     __syncwarp();
