@@ -426,7 +426,7 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
     vec = torch.randn(1, C, device=dev, generator=g).to(BF)
     pe = EmbedND(128, 10000, [16, 56, 56])(flux_position_ids(lt, grid, grid, device=dev))
     if world > 1:
-        block.sequence_parallel = SequenceParallel()
+        block.sequence_parallel = SequenceParallel(exchange=args.exchange)
         txt, img, pe = shard_joint_sequence(txt, img, pe, rank, world)
 
     def barrier():
@@ -466,11 +466,15 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"flux_double_stream_block hidden {C}, {H} heads x 128, {li} image + {lt} text tokens, "
                                    "batch 1 in total, weights N(0,0.02), seed 4",
-                       "parallelism": f"ulysses sequence-parallel x{world} (all-to-all on heads, NCCL)",
+                       "parallelism": f"ulysses sequence-parallel x{world} (head exchange: "
+                                      + ("stores into peer memory from the producing kernels"
+                                         if args.exchange == "peer" and world > 1 else "NCCL all-to-all") + ")",
                        "block_tflop": flop / 1e12, "tflops_per_gpu": flop * args.steps / (ms * 1e-3) / 1e12 / world},
             "gpu_launches": launches, "clocks": clocks,
         }), flush=True)
     if world > 1:
+        if block.sequence_parallel is not None:
+            block.sequence_parallel.close()
         dist.barrier()
         dist.destroy_process_group()
 
@@ -556,6 +560,9 @@ def main():
     ap.add_argument("--parallel", default="dp", choices=["dp", "ulysses"],
                     help="multi-GPU sharding: batch data-parallel (default, weak scaling) or Ulysses sequence parallelism "
                          "on a 16384+512-token block (strong scaling)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="--parallel ulysses: how heads and tokens are exchanged around attention: stores into peer "
+                         "memory from the producing kernels (default) or two NCCL all-to-alls")
     ap.add_argument("--sweep", default=None, help="sequence-length sweep with the reference benchmark scripts' shapes: "
                     "all | linear | attention | layer_norm | rms_norm | rope (--steps = timed calls per point)")
     ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")

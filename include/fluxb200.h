@@ -226,6 +226,63 @@ int fluxb_modulation_gate_proj(const void* resid, const void* mod, const void* p
 /* out = x * sigmoid(x), flat.  Replaces triton_kernels/ops/silu.py:5-13. */
 int fluxb_silu(const void* x, void* out, int64_t n, int dtype, fluxb_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Sequence-parallel (Ulysses) exchange over peer memory.  The reference has no multi-GPU path,
+ * so nothing in this section replaces a reference function; the entry points exist so that the
+ * two kernels on either side of the head all-to-all store straight into the consuming GPU's
+ * memory (plain global stores over NVLink; peers are never read, and never touched by TMA).
+ *
+ * An "arena" is a device allocation whose first fluxb_peer_header_bytes() bytes belong to the
+ * library (arrival flags written by the peers, this rank's epoch counters); the caller lays
+ * out its exchange buffers after the header.  One process per GPU: fluxb_peer_alloc + export
+ * on the owner, fluxb_peer_open on every other rank (CUDA IPC), then `arenas[r]` is rank r's
+ * arena as addressable from the calling process (its own allocation for r == rank).
+ * ------------------------------------------------------------------------------------- */
+int fluxb_peer_header_bytes(void);
+/* Allocates `bytes` (>= header) of zeroed device memory on the current device.  Setup only. */
+int fluxb_peer_alloc(int64_t bytes, void** ptr);
+int fluxb_peer_free(void* ptr);
+/* Writes the 64-byte IPC handle of an arena from fluxb_peer_alloc. */
+int fluxb_peer_export(const void* ptr, void* handle64);
+/* Maps another process's arena into this one (peer access enabled lazily). */
+int fluxb_peer_open(const void* handle64, void** ptr);
+int fluxb_peer_close(void* ptr);
+/*
+ * Barrier halves, stream-ordered, no host synchronisation, safe to capture in a CUDA graph (the
+ * epochs live in the arena).  fluxb_peer_signal: everything enqueued on `stream` before it is
+ * complete and visible to the other ranks once they pass the matching wait.  fluxb_peer_wait:
+ * returns (on the stream) when every rank has signalled `barrier` as many times as this rank
+ * has waited on it.  The wait is bounded (2 s): on expiry the device status word reports
+ * FLUXB_ERR_TIMEOUT with site 61 + barrier and the stream continues.  barrier: 0 or 1.
+ */
+int fluxb_peer_signal(const void* const* arenas, int n_ranks, int rank, int barrier, fluxb_stream_t stream);
+int fluxb_peer_wait(const void* const* arenas, int n_ranks, int rank, int barrier, fluxb_stream_t stream);
+
+/*
+ * fluxb_qkv_prep with one output base per head group: heads [g*heads_per_group,
+ * (g+1)*heads_per_group) of q land at group_bases[g] + b*o_sb + (h % heads_per_group)*o_sh +
+ * l*o_sl, those of k and v k_off and v_off elements further.  n_groups*heads_per_group == H,
+ * n_groups <= 8.  The bases may point into other ranks' arenas.
+ */
+int fluxb_qkv_prep_scatter(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
+                           const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
+                           const void* qscale1, const void* kscale1, const float* pe,
+                           void* const* group_bases, int n_groups, int64_t k_off, int64_t v_off,
+                           int64_t B, int64_t H, int64_t D, int64_t heads_per_group, int64_t o_sb,
+                           int64_t o_sh, int64_t o_sl, float eps, fluxb_stream_t stream);
+
+/*
+ * fluxb_attention with one output base per owner of query rows: row r goes to
+ * o_bases[r / rows_per_rank] + b*o_sb + h*o_sh + (r % rows_per_rank)*o_sl.  n_ranks <= 8,
+ * n_ranks*rows_per_rank >= Lq.  The bases may point into other ranks' arenas.
+ */
+int fluxb_attention_scatter(const void* q, const void* k, const void* v, void* const* o_bases,
+                            int n_ranks, int64_t rows_per_rank, int64_t B, int64_t H, int64_t Lq,
+                            int64_t Lk, int64_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl,
+                            int64_t k_sb, int64_t k_sh, int64_t k_sl, int64_t v_sb, int64_t v_sh,
+                            int64_t v_sl, int64_t o_sb, int64_t o_sh, int64_t o_sl, float sm_scale,
+                            fluxb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,8 @@
 """Ulysses sequence parallelism on real GPUs (needs at least two): each rank's shard of the
 sequence-parallel block output equals the corresponding rows of the single-GPU block output.
-Ranks are child processes over NCCL with NVLS switched off; a rank only leaves between steps."""
+Both exchanges are run: the two NCCL all-to-alls, and the peer-memory form in which the
+producing kernels store straight into the other GPU's arena.  Ranks are child processes over
+NCCL with NVLS switched off; a rank only leaves between steps, after a collective teardown."""
 import os
 import socket
 
@@ -25,6 +27,7 @@ def _rank_main(rank: int, world: int, port: int, q_out):
     try:
         from oracle import flux_oracle as O
         import triton_kernels_b200 as tk
+        from triton_kernels_b200 import _lib
         from triton_kernels_b200.parallel import SequenceParallel, shard_joint_sequence
 
         BF = torch.bfloat16
@@ -46,22 +49,28 @@ def _rank_main(rank: int, world: int, port: int, q_out):
         with torch.no_grad():
             want_img, want_txt = dblk(img, txt, vec, pe)
             want_x = sblk(torch.cat((txt, img), 1), vec, pe)
-            sp = SequenceParallel()
-            dblk.sequence_parallel = sblk.sequence_parallel = sp
             txt_l, img_l, pe_l = shard_joint_sequence(txt, img, pe, rank, world)
-            got_img, got_txt = dblk(img_l, txt_l, vec, pe_l)
-            got_x = sblk(torch.cat((txt_l, img_l), 1), vec, pe_l)
-        torch.cuda.synchronize()
-        Li, Ltl = img.shape[1] // world, Lt // world
-        rows_i = slice(rank * Li, (rank + 1) * Li)
-        rows_t = slice(rank * Ltl, (rank + 1) * Ltl)
+            Li, Ltl = img.shape[1] // world, Lt // world
+            rows_i = slice(rank * Li, (rank + 1) * Li)
+            rows_t = slice(rank * Ltl, (rank + 1) * Ltl)
 
-        def rel(a, b):
-            return float((a.float() - b.float()).norm() / b.float().norm())
+            def rel(a, b):
+                return float((a.float() - b.float()).norm() / b.float().norm())
 
-        # same kernels and weights; only the key order inside attention differs
-        errs = [rel(got_img, want_img[:, rows_i]), rel(got_txt, want_txt[:, rows_t]),
-                rel(got_x[:, :Ltl], want_x[:, rows_t]), rel(got_x[:, Ltl:], want_x[:, Lt:][:, rows_i])]
+            errs = []
+            for exchange in ("nccl", "peer"):
+                sp = SequenceParallel(exchange=exchange)
+                dblk.sequence_parallel = sblk.sequence_parallel = sp
+                for _ in range(3):  # several rounds: the arenas and their epochs are reused
+                    got_img, got_txt = dblk(img_l, txt_l, vec, pe_l)
+                    got_x = sblk(torch.cat((txt_l, img_l), 1), vec, pe_l)
+                    # same kernels and weights; only the key order inside attention differs
+                    errs += [rel(got_img, want_img[:, rows_i]), rel(got_txt, want_txt[:, rows_t]),
+                             rel(got_x[:, :Ltl], want_x[:, rows_t]), rel(got_x[:, Ltl:], want_x[:, Lt:][:, rows_i])]
+                torch.cuda.synchronize()
+                sp.close()
+        code, where = _lib.device_status()
+        assert code == 0, f"device status {code} at {where}"
         dist.barrier()
         q_out.put((rank, max(errs)))
     except Exception as e:  # noqa: BLE001

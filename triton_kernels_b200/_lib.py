@@ -52,6 +52,17 @@ SIGNATURES = {
     "fluxb_modulation_scale_shift": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _I, _P]),
     "fluxb_modulation_gate_proj": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _P]),
     "fluxb_silu": (_I, [_P, _P, _L, _I, _P]),
+    "fluxb_peer_header_bytes": (_I, []),
+    "fluxb_peer_alloc": (_I, [_L, POINTER(c_void_p)]),
+    "fluxb_peer_free": (_I, [_P]),
+    "fluxb_peer_export": (_I, [_P, _P]),
+    "fluxb_peer_open": (_I, [_P, POINTER(c_void_p)]),
+    "fluxb_peer_close": (_I, [_P]),
+    "fluxb_peer_signal": (_I, [POINTER(c_void_p), _I, _I, _I, _P]),
+    "fluxb_peer_wait": (_I, [POINTER(c_void_p), _I, _I, _I, _P]),
+    "fluxb_qkv_prep_scatter": (_I, [_P, _L, _L, _P, _P, _P, _L, _L, _P, _P, _P, POINTER(c_void_p), _I, _L, _L,
+                                    _L, _L, _L, _L, _L, _L, _L, _F, _P]),
+    "fluxb_attention_scatter": (_I, [_P, _P, _P, POINTER(c_void_p), _I, _L] + [_L] * 5 + [_L] * 12 + [_F, _P]),
 }
 
 _lib = None

@@ -39,6 +39,11 @@ struct Params {
   float scale_log2;
   uint32_t v_lbo, v_sbo;
   DeviceStatus* status;
+  // Scatter form (rows_per_rank > 0): query row r belongs to rank r / rows_per_rank and is
+  // stored at o_rank[that rank] + batch*o_sb + head*o_sh + (r % rows_per_rank)*o_sl; the bases
+  // may be other GPUs' memory (plain stores only).
+  int rows_per_rank;
+  __nv_bfloat16* o_rank[8];
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -360,6 +365,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       tc_fence_after_sync();
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + (int64_t)row * p.o_sl;
+      if (p.rows_per_rank > 0 && row < p.Lq) {
+        const int owner = row / p.rows_per_rank;
+        orow = p.o_rank[owner] + batch * p.o_sb + head * p.o_sh + (int64_t)(row - owner * p.rows_per_rank) * p.o_sl;
+      }
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
@@ -410,12 +419,21 @@ static uint32_t env_u32(const char* name, uint32_t dflt) {
   return (uint32_t)strtoul(s, nullptr, 0);
 }
 
-extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void* o, int64_t B,
-                               int64_t H, int64_t Lq, int64_t Lk, int64_t D, int64_t q_sb,
-                               int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
-                               int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
-                               int64_t o_sl, float sm_scale, fluxb_stream_t stream) {
+static int attention_impl(const void* q, const void* k, const void* v, void* o, int64_t B,
+                          int64_t H, int64_t Lq, int64_t Lk, int64_t D, int64_t q_sb,
+                          int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                          int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
+                          int64_t o_sl, float sm_scale, void* const* o_bases, int n_ranks,
+                          int64_t rows_per_rank, fluxb_stream_t stream) {
   using namespace fluxb::attn;
+  if (n_ranks > 0) {
+    if (n_ranks > 8 || !o_bases || rows_per_rank <= 0 || rows_per_rank * n_ranks < Lq || rows_per_rank > (1 << 30))
+      return set_error(FLUXB_ERR_BAD_ARG, "attention_scatter: need 1..8 output bases whose rows_per_rank rows cover Lq");
+    for (int i = 0; i < n_ranks; ++i)
+      if (!o_bases[i] || (reinterpret_cast<uintptr_t>(o_bases[i]) & 15))
+        return set_error(FLUXB_ERR_BAD_ARG, "attention_scatter: output base %d is null or misaligned", i);
+    o = o_bases[0];
+  }
   if (D != 128 && D != 64)
     return set_error(FLUXB_ERR_UNSUPPORTED, "attention: head_dim %lld (64 and 128 are built)", (long long)D);
   if (B < 0 || H < 0 || Lq < 0 || Lk < 0) return set_error(FLUXB_ERR_BAD_ARG, "attention: negative size");
@@ -449,6 +467,8 @@ extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void
   p.v_lbo = env_u32("FLUXB_ATTN_V_LBO", HALF_BYTES);
   p.v_sbo = env_u32("FLUXB_ATTN_V_SBO", 1024);
   p.status = device_status_ptr();
+  p.rows_per_rank = n_ranks > 0 ? (int)rows_per_rank : 0;
+  for (int i = 0; i < 8; ++i) p.o_rank[i] = i < n_ranks ? static_cast<__nv_bfloat16*>(o_bases[i]) : nullptr;
 
   // Every fourth pair of a row takes the polynomial exp2 unless FLUXB_ATTN_POLY=0 (all on MUFU).
   static const int poly_env = (int)env_u32("FLUXB_ATTN_POLY", 4);
@@ -466,4 +486,24 @@ extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
+}
+
+extern "C" int fluxb_attention(const void* q, const void* k, const void* v, void* o, int64_t B,
+                               int64_t H, int64_t Lq, int64_t Lk, int64_t D, int64_t q_sb,
+                               int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
+                               int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
+                               int64_t o_sl, float sm_scale, fluxb_stream_t stream) {
+  return attention_impl(q, k, v, o, B, H, Lq, Lk, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, v_sb, v_sh, v_sl, o_sb,
+                        o_sh, o_sl, sm_scale, nullptr, 0, 0, stream);
+}
+
+extern "C" int fluxb_attention_scatter(const void* q, const void* k, const void* v, void* const* o_bases,
+                                       int n_ranks, int64_t rows_per_rank, int64_t B, int64_t H, int64_t Lq,
+                                       int64_t Lk, int64_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl,
+                                       int64_t k_sb, int64_t k_sh, int64_t k_sl, int64_t v_sb, int64_t v_sh,
+                                       int64_t v_sl, int64_t o_sb, int64_t o_sh, int64_t o_sl, float sm_scale,
+                                       fluxb_stream_t stream) {
+  if (n_ranks <= 0) return set_error(FLUXB_ERR_BAD_ARG, "attention_scatter: no output bases");
+  return attention_impl(q, k, v, nullptr, B, H, Lq, Lk, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, v_sb, v_sh, v_sl,
+                        o_sb, o_sh, o_sl, sm_scale, o_bases, n_ranks, rows_per_rank, stream);
 }

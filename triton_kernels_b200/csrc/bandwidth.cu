@@ -622,6 +622,11 @@ struct QkvPrepArgs {
   // output addressing: element offset = b*o_sb + (h / hpg)*o_sg + (h % hpg)*o_sh + l*o_sl
   int64_t o_sb, o_sg, o_sh, o_sl, hpg;
   float eps;
+  // Scatter form (n_gbase > 0): head group g goes to gbase[g] (q), gbase[g] + k_off (k) and
+  // gbase[g] + v_off (v) instead of q/k/v + g*o_sg; the bases may be other GPUs' memory.
+  int n_gbase;
+  int64_t k_off, v_off;
+  __nv_bfloat16* gbase[8];
 };
 
 template <int HG>
@@ -667,7 +672,17 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
   for (int hh = 0; hh < HG; ++hh) {
     const int64_t h = h0 + hh;
     if (h >= a.H) continue;  // uniform across the block (depends on blockIdx.y only)
-    const int64_t out_off = b * a.o_sb + (h / a.hpg) * a.o_sg + (h % a.hpg) * a.o_sh + l * a.o_sl + lane16 * 8;
+    int64_t out_off = b * a.o_sb + (h % a.hpg) * a.o_sh + l * a.o_sl + lane16 * 8;
+    __nv_bfloat16* qk_base[2] = {a.q, a.k};
+    __nv_bfloat16* v_base = a.v;
+    if (a.n_gbase > 0) {
+      __nv_bfloat16* gb = a.gbase[h / a.hpg];
+      qk_base[0] = gb;
+      qk_base[1] = gb + a.k_off;
+      v_base = gb + a.v_off;
+    } else {
+      out_off += (h / a.hpg) * a.o_sg;
+    }
 #pragma unroll
     for (int part = 0; part < 2; ++part) {
       Vec<__nv_bfloat16> xv;
@@ -692,9 +707,9 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = x[j];
       }
-      if (active) store8<__nv_bfloat16>((part == 0 ? a.q : a.k) + out_off, o);
+      if (active) store8<__nv_bfloat16>(qk_base[part] + out_off, o);
     }
-    if (active) *reinterpret_cast<uint4*>(a.v + out_off) = raw[hh][2];
+    if (active) *reinterpret_cast<uint4*>(v_base + out_off) = raw[hh][2];
   }
 }
 
@@ -1032,17 +1047,18 @@ extern "C" int fluxb_rope(const void* q, const void* k, const float* pe, void* o
   return launch_status("rope");
 }
 
-extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
-                              const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
-                              const void* qscale1, const void* kscale1, const float* pe, void* q,
-                              void* k, void* v, int64_t B, int64_t H, int64_t D, int64_t heads_per_group,
-                              int64_t o_sb, int64_t o_sg, int64_t o_sh, int64_t o_sl, float eps,
-                              fluxb_stream_t stream) {
+static int qkv_prep_impl(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
+                         const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
+                         const void* qscale1, const void* kscale1, const float* pe, void* q,
+                         void* k, void* v, int64_t B, int64_t H, int64_t D, int64_t heads_per_group,
+                         int64_t o_sb, int64_t o_sg, int64_t o_sh, int64_t o_sl, float eps,
+                         void* const* group_bases, int n_groups, int64_t k_off, int64_t v_off,
+                         fluxb_stream_t stream) {
   if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "qkv_prep: head_dim %lld (only 128)", (long long)D);
   if (B < 0 || H <= 0 || L0 < 0 || L1 < 0) return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: bad sizes");
   const int64_t L = L0 + L1;
   if (B == 0 || L == 0) return FLUXB_OK;
-  if (!q || !k || !v || (L0 > 0 && !src0) || (L1 > 0 && !src1))
+  if ((n_groups == 0 && (!q || !k || !v)) || (L0 > 0 && !src0) || (L1 > 0 && !src1))
     return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep: null pointer");
   if ((qscale0 == nullptr) != (kscale0 == nullptr) || (L1 > 0 && ((qscale1 == nullptr) != (kscale1 == nullptr))) ||
       (L0 > 0 && L1 > 0 && ((qscale0 == nullptr) != (qscale1 == nullptr))))
@@ -1070,6 +1086,18 @@ extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const v
   a.k = static_cast<__nv_bfloat16*>(k);
   a.v = static_cast<__nv_bfloat16*>(v);
   a.B = B; a.H = H; a.L = L; a.eps = eps;
+  a.n_gbase = 0; a.k_off = 0; a.v_off = 0;
+  for (int i = 0; i < 8; ++i) a.gbase[i] = nullptr;
+  if (n_groups > 0) {
+    if (n_groups > 8 || heads_per_group <= 0 || heads_per_group * n_groups != H || !group_bases || k_off % 8 || v_off % 8)
+      return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep_scatter: need 1..8 groups of heads_per_group heads covering H, and offsets that are multiples of 8");
+    for (int i = 0; i < n_groups; ++i) {
+      if (!group_bases[i] || !aligned16(group_bases[i]))
+        return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep_scatter: group base %d is null or misaligned", i);
+      a.gbase[i] = static_cast<__nv_bfloat16*>(group_bases[i]);
+    }
+    a.n_gbase = n_groups; a.k_off = k_off; a.v_off = v_off;
+  }
   if (heads_per_group <= 0) {  // default: contiguous [B, H, L, D]
     a.hpg = H; a.o_sg = 0; a.o_sb = H * L * D; a.o_sh = L * D; a.o_sl = D;
   } else {
@@ -1081,6 +1109,28 @@ extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const v
   dim3 grid((unsigned)((B * L + 15) / 16), (unsigned)((H + HG - 1) / HG));
   qkv_prep_kernel<HG><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return launch_status("qkv_prep");
+}
+
+extern "C" int fluxb_qkv_prep(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
+                              const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
+                              const void* qscale1, const void* kscale1, const float* pe, void* q,
+                              void* k, void* v, int64_t B, int64_t H, int64_t D, int64_t heads_per_group,
+                              int64_t o_sb, int64_t o_sg, int64_t o_sh, int64_t o_sl, float eps,
+                              fluxb_stream_t stream) {
+  return qkv_prep_impl(src0, L0, ld0, qscale0, kscale0, src1, L1, ld1, qscale1, kscale1, pe, q, k, v, B, H, D,
+                       heads_per_group, o_sb, o_sg, o_sh, o_sl, eps, nullptr, 0, 0, 0, stream);
+}
+
+extern "C" int fluxb_qkv_prep_scatter(const void* src0, int64_t L0, int64_t ld0, const void* qscale0,
+                                      const void* kscale0, const void* src1, int64_t L1, int64_t ld1,
+                                      const void* qscale1, const void* kscale1, const float* pe,
+                                      void* const* group_bases, int n_groups, int64_t k_off, int64_t v_off,
+                                      int64_t B, int64_t H, int64_t D, int64_t heads_per_group, int64_t o_sb,
+                                      int64_t o_sh, int64_t o_sl, float eps, fluxb_stream_t stream) {
+  if (n_groups <= 0) return set_error(FLUXB_ERR_BAD_ARG, "qkv_prep_scatter: no groups");
+  return qkv_prep_impl(src0, L0, ld0, qscale0, kscale0, src1, L1, ld1, qscale1, kscale1, pe, nullptr, nullptr,
+                       nullptr, B, H, D, heads_per_group, o_sb, 0, o_sh, o_sl, eps, group_bases, n_groups, k_off,
+                       v_off, stream);
 }
 
 template <typename T>

@@ -27,6 +27,29 @@ def attention_into(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.T
     )
 
 
+def attention_scatter_into(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o_bases, n_ranks: int, rows_per_rank: int,
+    o_strides: tuple[int, int, int], sm_scale: float,
+) -> None:
+    """attention_into whose output rows go to one base address per owner of query rows (a ctypes
+    array of `n_ranks` device pointers, possibly into other GPUs' memory): row r of head h, batch
+    b lands at o_bases[r // rows_per_rank] + b*sb + h*sh + (r % rows_per_rank)*sl, with
+    (sb, sh, sl) = `o_strides` in elements."""
+    B, H, Lq, D = q.shape
+    Lk = k.shape[2]
+    for t in (q, k, v):
+        assert t.stride(3) == 1
+    _lib.check(
+        _lib.load().fluxb_attention_scatter(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), o_bases, n_ranks, rows_per_rank, B, H, Lq, Lk, D,
+            q.stride(0), q.stride(1), q.stride(2),
+            k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2),
+            *o_strides, float(sm_scale), _lib.stream_handle(),
+        )
+    )
+
+
 def scaled_dot_product_attention(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, sm_scale: float | None = None
 ) -> torch.Tensor:

@@ -27,12 +27,12 @@ import torch
 from torch import Tensor, nn
 
 from triton_kernels_b200 import _lib
-from triton_kernels_b200.kernels.attention import attention_into, scaled_dot_product_attention
+from triton_kernels_b200.kernels.attention import attention_into, attention_scatter_into, scaled_dot_product_attention
 from triton_kernels_b200.kernels.linear import linear, linear_grouped_into, linear_into
 from triton_kernels_b200.kernels.normalization import layer_norm_modulation_into
 from triton_kernels_b200.kernels.positional_embedding import apply_rope
 from triton_kernels_b200.modules.normalization import QKNorm
-from triton_kernels_b200.ops.fused import modulation_silu_linear, qkv_prepare_into
+from triton_kernels_b200.ops.fused import modulation_silu_linear, qkv_prepare_into, qkv_prepare_scatter
 
 LN_EPS = 1e-6
 
@@ -125,20 +125,42 @@ def _assemble_qkv(streams, pe: Tensor, num_heads: int):
     return q, k, v
 
 
-def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Tensor, sp=None) -> None:
-    """q/k/v assembly (split, QK-RMSNorm, RoPE, stream concat) + attention, written into `out`,
-    a [B, L, C] view with unit stride on the last dim (it may be a column range of a wider
-    buffer).  With a SequenceParallel handle the local tokens are exchanged for the local
-    heads before attention and back after it (triton_kernels_b200/parallel/ulysses.py)."""
+def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Tensor | None, sp=None) -> Tensor:
+    """q/k/v assembly (split, QK-RMSNorm, RoPE, stream concat) + attention.  The result is
+    written into `out`, a [B, L, C] view with unit stride on the last dim (it may be a column
+    range of a wider buffer), or, with out=None, into a buffer of the callee's choice; the
+    tensor holding it is returned.  With a SequenceParallel handle the local tokens are
+    exchanged for the local heads before attention and back after it
+    (triton_kernels_b200/parallel/ulysses.py)."""
     if sp is None or sp.world == 1:
         q, k, v = _assemble_qkv(streams, pe, num_heads)
         B, H, L, D = q.shape
+        if out is None:
+            out = torch.empty((B, L, H * D), device=q.device, dtype=q.dtype)
         attention_into(q, k, v, out.unflatten(2, (H, D)).permute(0, 2, 1, 3), scale)
-        return
+        return out
     B = streams[0][0].shape[0]
     L_loc = sum(s.shape[1] for s, _ in streams)
     D = streams[0][1].query_norm.scale.shape[0]
     dev, dt = streams[0][0].device, streams[0][0].dtype
+    if sp.exchange == "peer":
+        # Both exchanges happen inside the producing kernels, as stores into the peers' arenas.
+        pb = sp.peer_buffers(B, L_loc, num_heads, D, dt)
+        args = [(s, n.query_norm.scale.to(dt), n.key_norm.scale.to(dt)) for s, n in streams]
+        qkv_prepare_scatter(args, pe, pb.q_bases, pb.P, pb.Hp * D, 2 * pb.Hp * D, num_heads, D, pb.qkv_strides,
+                            eps=1e-6)
+        pb.arena.signal(0)
+        pb.arena.wait(0)
+        qv, kv, vv = (pb.recv[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [B, Hp, L, D] views
+        attention_scatter_into(qv, kv, vv, pb.o_bases, pb.P, L_loc, pb.o_strides, scale)
+        pb.arena.signal(1)
+        pb.arena.wait(1)
+        if out is None:
+            return pb.out  # valid until this rank's next attention with the same shape
+        out.copy_(pb.out)
+        return out
+    if out is None:
+        out = torch.empty((B, L_loc, num_heads * D), device=dev, dtype=dt)
     shape, layout = sp.send_layout(B, L_loc, num_heads, D)
     Hp = layout[0]
     send = torch.empty(shape, device=dev, dtype=dt)
@@ -152,6 +174,7 @@ def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Ten
     qv, kv, vv = (full[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [B, Hp, L, D] views
     attention_into(qv, kv, vv, o.view(B, L, Hp, D).permute(0, 2, 1, 3), scale)
     sp.heads_to_tokens(o, out)
+    return out
 
 
 def _ln_mod(x: Tensor, packed_mod: Tensor, chunk_shift: int) -> Tensor:
@@ -289,9 +312,8 @@ class DoubleStreamBlock(nn.Module):
             dict(x2d=h.view(B * L, C), w=a.qkv.weight, b=a.qkv.bias, y=o.view(B * L, 3 * C))
             for h, a, o, L in zip(h1, attns, qkvs, Ls)])
 
-        attn = torch.empty((B, Lt + Li, C), device=dev, dtype=dt)
-        _joint_attention([(qkvs[0], self.txt_attn.norm), (qkvs[1], self.img_attn.norm)], pe, H, D**-0.5, attn,
-                         self.sequence_parallel)
+        attn = _joint_attention([(qkvs[0], self.txt_attn.norm), (qkvs[1], self.img_attn.norm)], pe, H, D**-0.5,
+                                None, self.sequence_parallel)
 
         # proj + gate/residual: the rows of one stream of one batch item are one strided 2-D block
         x1 = [torch.empty_like(x) for x in xs]

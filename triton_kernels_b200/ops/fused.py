@@ -122,6 +122,42 @@ def qkv_prepare_into(
     )
 
 
+def qkv_prepare_scatter(
+    streams: list[tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None]],
+    pe: torch.Tensor | None,
+    group_bases,
+    n_groups: int,
+    k_off: int,
+    v_off: int,
+    num_heads: int,
+    head_dim: int,
+    strides: tuple[int, int, int],
+    eps: float = 1e-6,
+) -> None:
+    """qkv_prepare_into with one output base address per head group (a ctypes array of
+    `n_groups` device pointers, possibly into other GPUs' memory): q of head h, token l, batch b
+    lands at group_bases[h // hpg] + b*sb + (h % hpg)*sh + l*sl with (sb, sh, sl) = `strides` in
+    elements and hpg = num_heads // n_groups; k and v lie k_off / v_off elements further."""
+    assert 1 <= len(streams) <= 2
+    B = streams[0][0].shape[0]
+    args = []
+    for src, qs, ks in streams:
+        assert src.stride(2) == 1 and (src.shape[0] == 1 or src.stride(0) == src.shape[1] * src.stride(1))
+        args += [_lib.ptr(src), src.shape[1], src.stride(1), _lib.ptr(qs), _lib.ptr(ks)]
+    if len(streams) == 1:
+        args += [None, 0, 0, None, None]
+    pe_c = None
+    if pe is not None:
+        pe_c = pe if (pe.dtype == torch.float32 and pe.is_contiguous()) else pe.to(torch.float32).contiguous()
+    sb, sh, sl = strides
+    _lib.check(
+        _lib.load().fluxb_qkv_prep_scatter(
+            *args, _lib.ptr(pe_c), group_bases, n_groups, k_off, v_off, B, num_heads, head_dim,
+            num_heads // n_groups, sb, sh, sl, eps, _lib.stream_handle()
+        )
+    )
+
+
 def qkv_prepare(
     qkv_streams: list[torch.Tensor],
     num_heads: int,

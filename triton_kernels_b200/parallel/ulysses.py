@@ -21,6 +21,14 @@ before the exchange — which is how the assembly kernel is called.
 
 The exchange functions are plain torch.distributed calls on whatever device the tensors live
 on, so the layout logic is exercised on CPU ranks (gloo) as well as on GPUs (NCCL).
+
+With `exchange="peer"` (GPUs of one NVSwitch box) neither all-to-all is a separate step: the
+assembly kernel stores each head group straight into the arena of the rank that will attend
+over it, laid out as [B, L, 3, H/P, D], and the attention kernel stores each query row straight
+into the arena of the rank that owns the token, laid out as [B, L_loc, H*D]
+(triton_kernels_b200/parallel/peer.py).  Two flag barriers per attention order the stores:
+one after the assembly (all q/k/v have arrived), one after attention (all outputs have arrived;
+it also tells the peers that this rank's receive buffer may be overwritten again).
 """
 from __future__ import annotations
 
@@ -32,10 +40,26 @@ from torch import Tensor
 class SequenceParallel:
     """Process-group handle plus the two layout-changing exchanges."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, exchange: str = "nccl"):
+        assert exchange in ("nccl", "peer")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self.exchange = exchange
+        self._peer: dict = {}
+
+    # ---- peer-memory exchange ------------------------------------------------------------
+    def peer_buffers(self, B: int, L_loc: int, H: int, D: int, dtype: torch.dtype):
+        """Arena and address tables for one problem shape, created (collectively) on first use."""
+        key = (B, L_loc, H, D, dtype)
+        if key not in self._peer:
+            self._peer[key] = _PeerBuffers(self, B, L_loc, H, D, dtype)
+        return self._peer[key]
+
+    def close(self) -> None:
+        for pb in self._peer.values():
+            pb.arena.close()
+        self._peer = {}
 
     # ---- token-sharded -> head-sharded -------------------------------------------------
     def send_layout(self, B: int, L_loc: int, H: int, D: int) -> tuple[tuple[int, ...], tuple[int, int, int, int, int]]:
@@ -73,6 +97,43 @@ class SequenceParallel:
             out = torch.empty((B, L_loc, P * W), device=o.device, dtype=o.dtype)
         out.unflatten(2, (P, W)).copy_(recv.permute(1, 2, 0, 3))
         return out
+
+
+class _PeerBuffers:
+    """One arena per rank holding, after the library header,
+      recv [B, P*L_loc, 3, Hp, D]   q|k|v of all tokens for this rank's Hp heads, rows ordered
+                                    by source rank
+      out  [B, L_loc, H*D]          attention output of all heads for this rank's tokens
+    plus the address tables the scatter kernels take: where this rank's rows start in every
+    rank's `recv`, and where this rank's head columns start in every rank's `out`."""
+
+    def __init__(self, sp: SequenceParallel, B: int, L_loc: int, H: int, D: int, dtype: torch.dtype):
+        import ctypes
+
+        from .peer import PeerArena
+
+        P = sp.world
+        assert H % P == 0, f"{H} heads cannot be split over {P} ranks"
+        Hp = H // P
+        es = torch.empty((), dtype=dtype).element_size()
+        self.row = 3 * Hp * D  # elements per token in recv
+        recv_bytes = B * P * L_loc * self.row * es
+        out_bytes = B * L_loc * H * D * es
+        recv_bytes_padded = (recv_bytes + 255) // 256 * 256
+        self.arena = PeerArena(recv_bytes_padded + out_bytes, sp.group)
+        self.recv = self.arena.local_view(0, (B, P * L_loc, 3, Hp, D), dtype)
+        self.out = self.arena.local_view(recv_bytes_padded, (B, L_loc, H * D), dtype)
+        self.P, self.Hp, self.L_loc = P, Hp, L_loc
+        # head group g of this rank's tokens -> rank g's recv, rows [rank*L_loc, (rank+1)*L_loc)
+        self.q_bases = (ctypes.c_void_p * P)(
+            *[self.arena.address(g, sp.rank * L_loc * self.row * es) for g in range(P)]
+        )
+        self.qkv_strides = (P * L_loc * self.row, D, self.row)  # batch, head, token (elements)
+        # rows of rank r -> rank r's out, columns of this rank's heads
+        self.o_bases = (ctypes.c_void_p * P)(
+            *[self.arena.address(r, recv_bytes_padded + sp.rank * Hp * D * es) for r in range(P)]
+        )
+        self.o_strides = (L_loc * H * D, D, H * D)  # batch, head, row (elements)
 
 
 def shard_joint_sequence(txt: Tensor, img: Tensor, pe: Tensor, rank: int, world: int):
