@@ -92,3 +92,51 @@ def test_shard_helpers_partition_exactly():
     assert seen_t == txt.flatten().tolist() and seen_i == img.flatten().tolist()
     with pytest.raises(AssertionError):
         shard_joint_sequence(txt, img, pe, 0, 3)
+
+
+@pytest.mark.parametrize("B,P", [(1, 2), (2, 4)])
+def test_peer_exchange_layout_places_every_element_once(B, P):
+    """The address tables of the peer exchange, replayed on CPU: every rank "stores" its q/k/v
+    with the scatter kernel's addressing rule into flat per-rank arenas, attention is done per
+    head group on what arrived, its output is "stored" with the attention kernel's rule, and
+    every rank must end up with full-sequence attention for its own tokens."""
+    import torch.nn.functional as F
+
+    from triton_kernels_b200.parallel import peer_exchange_layout
+
+    H, D, L_loc = 4, 8, 6
+    L = P * L_loc
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(B, H, L, D, generator=g) for _ in range(3))
+    # rank-major token order is the global order here
+    want = F.scaled_dot_product_attention(q, k, v).permute(0, 2, 1, 3).reshape(B, L, H * D)
+    lays = [peer_exchange_layout(B, L_loc, H, D, P, r, 4) for r in range(P)]
+    arenas = [torch.full((lays[0]["nbytes"] // 4,), float("nan")) for _ in range(P)]
+    Hp = lays[0]["Hp"]
+    for r, lay in enumerate(lays):  # assembly kernel of rank r
+        sb, sh, sl = lay["qkv_strides"]
+        for h in range(H):
+            grp, hh = divmod(h, Hp)
+            base = lay["q_offsets"][grp] // 4
+            for part, t in ((0, q), (lay["k_off"], k), (lay["v_off"], v)):
+                for b in range(B):
+                    for l in range(L_loc):
+                        o = base + part + b * sb + hh * sh + l * sl
+                        arenas[grp][o:o + D] = t[b, h, r * L_loc + l]
+    for r, lay in enumerate(lays):  # attention of rank r over its head group, then its stores
+        n = B * L * 3 * Hp * D
+        recv = arenas[r][:n].view(lay["recv_shape"])
+        assert not torch.isnan(recv).any()
+        qv, kv, vv = (recv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        o = F.scaled_dot_product_attention(qv, kv, vv)  # [B, Hp, L, D]
+        sb, sh, sl = lay["o_strides"]
+        for row in range(L):
+            owner, lr = divmod(row, L_loc)
+            for b in range(B):
+                for hh in range(Hp):
+                    a = lay["o_offsets"][owner] // 4 + b * sb + hh * sh + lr * sl
+                    arenas[owner][a:a + D] = o[b, hh, row]
+    for r, lay in enumerate(lays):
+        off = lay["out_offset"] // 4
+        out = arenas[r][off:off + B * L_loc * H * D].view(lay["out_shape"])
+        torch.testing.assert_close(out, want[:, r * L_loc:(r + 1) * L_loc], atol=1e-5, rtol=1e-5)

@@ -147,7 +147,7 @@ def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Ten
         # Both exchanges happen inside the producing kernels, as stores into the peers' arenas.
         pb = sp.peer_buffers(B, L_loc, num_heads, D, dt)
         args = [(s, n.query_norm.scale.to(dt), n.key_norm.scale.to(dt)) for s, n in streams]
-        qkv_prepare_scatter(args, pe, pb.q_bases, pb.P, pb.Hp * D, 2 * pb.Hp * D, num_heads, D, pb.qkv_strides,
+        qkv_prepare_scatter(args, pe, pb.q_bases, pb.P, pb.k_off, pb.v_off, num_heads, D, pb.qkv_strides,
                             eps=1e-6)
         pb.arena.signal(0)
         pb.arena.wait(0)

@@ -99,13 +99,36 @@ class SequenceParallel:
         return out
 
 
+def peer_exchange_layout(B: int, L_loc: int, H: int, D: int, P: int, rank: int, elem_size: int) -> dict:
+    """Where things live in the arenas of the peer exchange, as seen from `rank` (pure
+    arithmetic; offsets in bytes after the arena header, strides in elements).
+
+      recv [B, P*L_loc, 3, Hp, D]  q|k|v of all tokens for the owner's Hp = H/P heads, rows ordered
+                                   by source rank
+      out  [B, L_loc, H*D]         attention output of all heads for the owner's tokens
+
+    q_offsets[g]: where this rank's rows start in rank g's recv (q of its first token; k and v
+    lie k_off / v_off elements further).  o_offsets[r]: where this rank's head columns start in
+    rank r's out."""
+    assert H % P == 0, f"{H} heads cannot be split over {P} ranks"
+    Hp = H // P
+    row = 3 * Hp * D
+    recv_bytes = (B * P * L_loc * row * elem_size + 255) // 256 * 256
+    out_bytes = B * L_loc * H * D * elem_size
+    return dict(
+        Hp=Hp, row=row,
+        recv_shape=(B, P * L_loc, 3, Hp, D), out_shape=(B, L_loc, H * D),
+        recv_offset=0, out_offset=recv_bytes, nbytes=recv_bytes + out_bytes,
+        q_offsets=[rank * L_loc * row * elem_size] * P, k_off=Hp * D, v_off=2 * Hp * D,
+        qkv_strides=(P * L_loc * row, D, row),  # batch, head, token
+        o_offsets=[recv_bytes + rank * Hp * D * elem_size] * P,
+        o_strides=(L_loc * H * D, D, H * D),  # batch, head, row
+    )
+
+
 class _PeerBuffers:
-    """One arena per rank holding, after the library header,
-      recv [B, P*L_loc, 3, Hp, D]   q|k|v of all tokens for this rank's Hp heads, rows ordered
-                                    by source rank
-      out  [B, L_loc, H*D]          attention output of all heads for this rank's tokens
-    plus the address tables the scatter kernels take: where this rank's rows start in every
-    rank's `recv`, and where this rank's head columns start in every rank's `out`."""
+    """One arena per rank laid out by peer_exchange_layout, plus the address tables the scatter
+    kernels take."""
 
     def __init__(self, sp: SequenceParallel, B: int, L_loc: int, H: int, D: int, dtype: torch.dtype):
         import ctypes
@@ -113,27 +136,16 @@ class _PeerBuffers:
         from .peer import PeerArena
 
         P = sp.world
-        assert H % P == 0, f"{H} heads cannot be split over {P} ranks"
-        Hp = H // P
-        es = torch.empty((), dtype=dtype).element_size()
-        self.row = 3 * Hp * D  # elements per token in recv
-        recv_bytes = B * P * L_loc * self.row * es
-        out_bytes = B * L_loc * H * D * es
-        recv_bytes_padded = (recv_bytes + 255) // 256 * 256
-        self.arena = PeerArena(recv_bytes_padded + out_bytes, sp.group)
-        self.recv = self.arena.local_view(0, (B, P * L_loc, 3, Hp, D), dtype)
-        self.out = self.arena.local_view(recv_bytes_padded, (B, L_loc, H * D), dtype)
-        self.P, self.Hp, self.L_loc = P, Hp, L_loc
-        # head group g of this rank's tokens -> rank g's recv, rows [rank*L_loc, (rank+1)*L_loc)
-        self.q_bases = (ctypes.c_void_p * P)(
-            *[self.arena.address(g, sp.rank * L_loc * self.row * es) for g in range(P)]
-        )
-        self.qkv_strides = (P * L_loc * self.row, D, self.row)  # batch, head, token (elements)
-        # rows of rank r -> rank r's out, columns of this rank's heads
-        self.o_bases = (ctypes.c_void_p * P)(
-            *[self.arena.address(r, recv_bytes_padded + sp.rank * Hp * D * es) for r in range(P)]
-        )
-        self.o_strides = (L_loc * H * D, D, H * D)  # batch, head, row (elements)
+        lay = peer_exchange_layout(B, L_loc, H, D, P, sp.rank, torch.empty((), dtype=dtype).element_size())
+        self.arena = PeerArena(lay["nbytes"], sp.group)
+        self.recv = self.arena.local_view(lay["recv_offset"], lay["recv_shape"], dtype)
+        self.out = self.arena.local_view(lay["out_offset"], lay["out_shape"], dtype)
+        self.P, self.Hp, self.L_loc = P, lay["Hp"], L_loc
+        self.k_off, self.v_off = lay["k_off"], lay["v_off"]
+        self.q_bases = (ctypes.c_void_p * P)(*[self.arena.address(g, off) for g, off in enumerate(lay["q_offsets"])])
+        self.qkv_strides = lay["qkv_strides"]
+        self.o_bases = (ctypes.c_void_p * P)(*[self.arena.address(r, off) for r, off in enumerate(lay["o_offsets"])])
+        self.o_strides = lay["o_strides"]
 
 
 def shard_joint_sequence(txt: Tensor, img: Tensor, pe: Tensor, rank: int, world: int):
