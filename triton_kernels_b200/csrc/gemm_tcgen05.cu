@@ -194,7 +194,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp walks the loop and an elected lane issues (warp-uniform descriptors).
+    {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -203,24 +204,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, 2))) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3))) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint64_t adesc = make_smem_desc(a_addr, 16, 1024);
           const uint64_t bdesc = make_smem_desc(a_addr + A_BYTES, 16, 1024);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            // 16 bf16 along K = 32 bytes = 2 descriptor address units
-            umma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k) {
+              // 16 bf16 along K = 32 bytes = 2 descriptor address units
+              umma_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(&empty_bar[stage]);
           }
-          umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&acc_full[acc]);
+        if (ok && elect_one()) umma_commit(&acc_full[acc]);
       }
     }
     __syncwarp();
