@@ -450,10 +450,41 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
         launches = _lib.kernel_calls - calls0
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop()
+    exchange_info = None
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+        # Bytes each GPU sends over NVLink per block: (P-1)/P of its q, k, v and of its attention output.
+        l_loc = (li + lt) // world
+        sent = (world - 1) / world * (3 + 1) * l_loc * C * 2
+        exchange_info = {"nvlink_bytes_sent_per_gpu_per_step": sent}
+        if args.exchange == "peer":
+            # The assembly kernel alone (it IS the q/k/v transfer): event-timed, barriers kept in step.
+            from triton_kernels_b200.ops.fused import qkv_prepare_scatter
+            sp = block.sequence_parallel
+            pb = sp.peer_buffers(1, l_loc, H, C // H, BF)
+            qkv_t = torch.randn(1, lt // world, 3 * C, device=dev, generator=g).to(BF)
+            qkv_i = torch.randn(1, li // world, 3 * C, device=dev, generator=g).to(BF)
+            streams = [(qkv_t, block.txt_attn.norm.query_norm.scale, block.txt_attn.norm.key_norm.scale),
+                       (qkv_i, block.img_attn.norm.query_norm.scale, block.img_attn.norm.key_norm.scale)]
+            times = []
+            for _ in range(8):
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                dist.barrier()
+                a0.record()
+                qkv_prepare_scatter(streams, pe, pb.q_bases, pb.P, pb.k_off, pb.v_off, H, C // H, pb.qkv_strides)
+                a1.record()
+                for b in (0, 1):
+                    pb.arena.signal(b)
+                    pb.arena.wait(b)
+                torch.cuda.synchronize()
+                times.append(a0.elapsed_time(a1))
+            tt = torch.tensor([sorted(times)[len(times) // 2]], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            qkv_sent = (world - 1) / world * 3 * l_loc * C * 2
+            exchange_info.update({"assembly_scatter_kernel_ms": float(tt.item()),
+                                  "assembly_scatter_nvlink_gbs_per_gpu": qkv_sent / (float(tt.item()) * 1e-3) / 1e9})
     code, where = _lib.device_status()
     if code != 0:
         raise SystemExit(f"device status word reports error {code} at {where}")
@@ -469,7 +500,8 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
                        "parallelism": f"ulysses sequence-parallel x{world} (head exchange: "
                                       + ("stores into peer memory from the producing kernels"
                                          if args.exchange == "peer" and world > 1 else "NCCL all-to-all") + ")",
-                       "block_tflop": flop / 1e12, "tflops_per_gpu": flop * args.steps / (ms * 1e-3) / 1e12 / world},
+                       "block_tflop": flop / 1e12, "tflops_per_gpu": flop * args.steps / (ms * 1e-3) / 1e12 / world,
+                       "exchange": exchange_info},
             "gpu_launches": launches, "clocks": clocks,
         }), flush=True)
     if world > 1:
