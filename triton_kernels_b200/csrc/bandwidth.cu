@@ -633,7 +633,12 @@ template <int HG>
 __global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
   constexpr int D = 128;
   const int lane16 = threadIdx.x & 15;
-  const int64_t tok = (int64_t)blockIdx.x * (blockDim.x / 16) + threadIdx.x / 16;  // b * L + l
+  // Plain form: blockIdx.x walks token blocks, blockIdx.y head blocks.  Scatter form: the other
+  // way round, so that blocks that run at the same time write to different destinations (local
+  // memory and every peer) instead of one destination after the other.
+  const unsigned tok_blk = a.n_gbase > 0 ? blockIdx.y : blockIdx.x;
+  const unsigned head_blk = a.n_gbase > 0 ? blockIdx.x : blockIdx.y;
+  const int64_t tok = (int64_t)tok_blk * (blockDim.x / 16) + threadIdx.x / 16;  // b * L + l
   const bool active = tok < a.B * a.L;
   const int64_t t = active ? tok : a.B * a.L - 1;
   const int64_t b = t / a.L;
@@ -657,7 +662,7 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
     load8<__nv_bfloat16>(a.kscale[s] + lane16 * 8, wk);
   }
 
-  const int64_t h0 = (int64_t)blockIdx.y * HG;
+  const int64_t h0 = (int64_t)head_blk * HG;
   uint4 raw[HG][3];
 #pragma unroll
   for (int hh = 0; hh < HG; ++hh) {
@@ -671,7 +676,7 @@ __global__ void __launch_bounds__(256) qkv_prep_kernel(QkvPrepArgs a) {
 #pragma unroll
   for (int hh = 0; hh < HG; ++hh) {
     const int64_t h = h0 + hh;
-    if (h >= a.H) continue;  // uniform across the block (depends on blockIdx.y only)
+    if (h >= a.H) continue;  // uniform across the block (depends on the head block only)
     int64_t out_off = b * a.o_sb + (h % a.hpg) * a.o_sh + l * a.o_sl + lane16 * 8;
     __nv_bfloat16* qk_base[2] = {a.q, a.k};
     __nv_bfloat16* v_base = a.v;
@@ -1107,6 +1112,10 @@ static int qkv_prep_impl(const void* src0, int64_t L0, int64_t ld0, const void* 
   }
   constexpr int HG = 4;
   dim3 grid((unsigned)((B * L + 15) / 16), (unsigned)((H + HG - 1) / HG));
+  if (a.n_gbase > 0) {
+    if (grid.x > 65535) return set_error(FLUXB_ERR_UNSUPPORTED, "qkv_prep_scatter: more than 1048560 tokens per call");
+    grid = dim3(grid.y, grid.x);
+  }
   qkv_prep_kernel<HG><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return launch_status("qkv_prep");
 }
