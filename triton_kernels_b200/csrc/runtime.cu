@@ -94,7 +94,7 @@ int encode_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_
 
 }  // namespace fluxb
 
-extern "C" int fluxb_version(void) { return 100; }
+extern "C" int fluxb_version(void) { return 101; }  // 101: peer-exchange entry points
 
 extern "C" const char* fluxb_last_error(void) { return fluxb::g_err; }
 

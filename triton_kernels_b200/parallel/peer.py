@@ -44,10 +44,10 @@ class PeerArena:
         self.header = lib.fluxb_peer_header_bytes()
         self.nbytes = self.header + ((nbytes + 255) // 256) * 256
         own = c_void_p()
-        _lib.check(lib.fluxb_peer_alloc(self.nbytes, ctypes.byref(own)))
+        _lib.check(lib.fluxb_peer_alloc(self.nbytes, ctypes.byref(own)), launches=False)
         self._own = own.value
         handle = ctypes.create_string_buffer(64)
-        _lib.check(lib.fluxb_peer_export(self._own, handle))
+        _lib.check(lib.fluxb_peer_export(self._own, handle), launches=False)
         handles: list = [None] * self.world
         dist.all_gather_object(handles, bytes(handle.raw), group=group)
         self.ptrs: list[int] = []
@@ -57,7 +57,7 @@ class PeerArena:
                 self.ptrs.append(self._own)
                 continue
             p = c_void_p()
-            _lib.check(lib.fluxb_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)))
+            _lib.check(lib.fluxb_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)), launches=False)
             self.ptrs.append(p.value)
             self._opened.append(p.value)
         self.c_ptrs = (c_void_p * self.world)(*self.ptrs)
