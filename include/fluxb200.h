@@ -226,6 +226,31 @@ int fluxb_modulation_gate_proj(const void* resid, const void* mod, const void* p
 /* out = x * sigmoid(x), flat.  Replaces triton_kernels/ops/silu.py:5-13. */
 int fluxb_silu(const void* x, void* out, int64_t n, int dtype, fluxb_stream_t stream);
 
+/*
+ * The q|k|v projections of up to four token streams (same weights' shape, different operands
+ * and row counts) in one launch, with everything between the projection and attention done in
+ * the GEMM epilogue: per-head RMS norm of q and k with the stream's scales, rotation with the
+ * stream's rows of pe, head-major layout and stream concatenation.  Replaces, fused, the
+ * qkv Linear of triton_kernels/modules/blocks.py:33,47 plus the rearrange / QKNorm / torch.cat /
+ * apply_rope sequence at triton_kernels/modules/blocks.py:113-119,148-162.
+ *   problems[i]: x [B*L_i, K] (ldx), w [3*H*D, K] (ldw), bias [3*H*D] or NULL, M = B*L_i,
+ *                rows_per_batch = L_i (a multiple of 128); the other fields are ignored.
+ *   streams[i]:  pe fp32 [L_total, D/2, 2, 2] or NULL; q_scale, k_scale bf16 [D] or both NULL;
+ *                row_offset = position of the stream's first token in the joint sequence (a
+ *                multiple of 128).
+ *   qkv_out: bf16 [3, B, H, L_total, D].  D must be 128.  The projection is rounded to bf16
+ *   before the norm, as the reference's bf16 Linear output is.
+ */
+typedef struct {
+  const float* pe;
+  const void* q_scale;
+  const void* k_scale;
+  int64_t row_offset;
+} fluxb_qkv_stream;
+int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams, int count,
+                             int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K, void* qkv_out,
+                             float eps, fluxb_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * Sequence-parallel (Ulysses) exchange over peer memory.  The reference has no multi-GPU path,
  * so nothing in this section replaces a reference function; the entry points exist so that the

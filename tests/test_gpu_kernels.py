@@ -350,3 +350,60 @@ def test_device_status_is_clean(tk):
     from triton_kernels_b200 import _lib
 
     assert _lib.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("B,Lt,Li,bias", [(1, 128, 384, False), (2, 256, 128, True)])
+def test_linear_qkv_grouped_matches_projection_plus_assembly(tk, B, Lt, Li, bias):
+    """The q|k|v projection with norm, rotation and head-major layout in its epilogue against the
+    plain projection followed by the assembly kernel."""
+    from triton_kernels_b200 import ops
+    from triton_kernels_b200.kernels.linear import linear_qkv_grouped_into
+
+    g = gen(61)
+    H, D, K = 4, 128, 512
+    C3 = 3 * H * D
+    xs = [torch.randn(B, L, K, generator=g).to(BF).cuda() for L in (Lt, Li)]
+    ws = [(torch.randn(C3, K, generator=g) * 0.05).to(BF).cuda() for _ in range(2)]
+    bs = [(torch.randn(C3, generator=g) * 0.1).to(BF).cuda() if bias else None for _ in range(2)]
+    qs = [(1 + 0.1 * torch.randn(D, generator=g)).to(BF).cuda() for _ in range(2)]
+    ks = [(1 + 0.1 * torch.randn(D, generator=g)).to(BF).cuda() for _ in range(2)]
+    L = Lt + Li
+    pe = torch.randn(1, 1, L, D // 2, 2, 2, generator=g).cuda()
+    out = torch.zeros(3, B, H, L, D, dtype=BF, device="cuda")
+    linear_qkv_grouped_into([dict(x=x, w=w, b=b, q_scale=q_, k_scale=k_) for x, w, b, q_, k_ in zip(xs, ws, bs, qs, ks)],
+                            pe, out)
+    qkvs = [tk.linear(x, w, b) for x, w, b in zip(xs, ws, bs)]
+    q, k, v = ops.qkv_prepare(qkvs, H, qs, ks, pe)
+    torch.cuda.synchronize()
+    assert torch.equal(out[2], v)
+    torch.testing.assert_close(out[0].float(), q.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(out[1].float(), k.float(), atol=2e-2, rtol=2e-2)
+    # without scales and table it is the projection re-laid out
+    out2 = torch.zeros_like(out)
+    linear_qkv_grouped_into([dict(x=x, w=w, b=b) for x, w, b in zip(xs, ws, bs)], None, out2)
+    q2, k2, v2 = ops.qkv_prepare(qkvs, H)
+    torch.cuda.synchronize()
+    assert torch.equal(out2[0], q2) and torch.equal(out2[1], k2) and torch.equal(out2[2], v2)
+
+
+def test_double_block_fused_qkv_epilogue_matches_unfused(tk):
+    g = gen(62)
+    C, H, Lt, Li = 512, 4, 128, 256
+    blk = tk.DoubleStreamBlock(C, H, 4.0).to(BF).cuda()
+    with torch.no_grad():
+        for name, p in blk.named_parameters():
+            p.copy_((torch.randn(p.shape, generator=g) * (0.1 if name.endswith("scale") else 0.03)
+                     + (1.0 if name.endswith("scale") else 0.0)).to(BF))
+    img = torch.randn(1, Li, C, generator=g).to(BF).cuda()
+    txt = torch.randn(1, Lt, C, generator=g).to(BF).cuda()
+    vec = torch.randn(1, C, generator=g).to(BF).cuda()
+    pe = torch.randn(1, 1, Lt + Li, C // H // 2, 2, 2, generator=g).cuda()
+    with torch.no_grad():
+        blk.fuse_qkv_epilogue = True
+        a_img, a_txt = blk(img, txt, vec, pe)
+        blk.fuse_qkv_epilogue = False
+        b_img, b_txt = blk(img, txt, vec, pe)
+    torch.cuda.synchronize()
+    for a, b in ((a_img, b_img), (a_txt, b_txt)):
+        rel = float((a.float() - b.float()).norm() / b.float().norm())
+        assert rel < 3e-3, rel

@@ -51,7 +51,15 @@ struct Params {
   int pair_stages;  // CTA-pair kernel: ring depth in use (<= gemm2::STAGES)
   int raster_band_n, raster_group;  // tile order, see tile_coords
   DeviceStatus* status;
+  // EPI_QKV_HEADS (CTA-pair kernel only): the N = 3*heads*128 columns are q | k | v of `heads`
+  // heads; q and k rows are RMS-normalised per head with qk_scale[0/1] (if given) and rotated
+  // with pe (if given), and everything is stored head-major through the 5-D map in tm_y.
+  const float* pe;                     // [l_total, 64, 2, 2]
+  const __nv_bfloat16* qk_scale[2];    // [128] each
+  int row_offset, heads, l_total;      // joint position of this problem's first token
+  float eps;
 };
+constexpr int EPI_QKV_HEADS = 3;  // internal epilogue code, set by fluxb_linear_qkv_grouped
 
 // Tile order.  The tiles running at one time form a gm x gn rectangle of the output; all of
 // them walk K in step, so each x row-block and w row-block is fetched from HBM once per
@@ -323,6 +331,128 @@ __device__ __forceinline__ int find_problem(const Grouped& g, int tile) {
   return i;
 }
 
+// Epilogue of one 128-row x 256-column tile (two heads of q, of k or of v) for EPI_QKV_HEADS:
+// bias, rounding to bf16 (the projection's output precision in the reference), per-head RMS norm
+// and rotation for q and k in fp32 with one rounding at the end, head-major 5-D TMA stores at
+// (d, l, head, batch, part).  One thread owns one row.  The row's sum of squares is taken in a
+// first sweep over the accumulator; the second sweep goes 16 columns at a time for BOTH heads,
+// because the rotation entries depend on the row and the pair only: each batch of eight
+// pe entries is loaded once and used for the two heads.  Staging tile hh collects head hh.
+__device__ __forceinline__ void qkv_load16(const Params& p, uint32_t taddr, int col, float (&x)[16]) {
+  uint32_t r[16];
+  tmem_ld_x16(taddr, r);
+  tmem_wait_ld();
+#pragma unroll
+  for (int e = 0; e < 16; ++e) x[e] = __uint_as_float(r[e]);
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col + j * 8));
+      x[j * 8 + 0] += bf16_lo(bv.x); x[j * 8 + 1] += bf16_hi(bv.x); x[j * 8 + 2] += bf16_lo(bv.y); x[j * 8 + 3] += bf16_hi(bv.y);
+      x[j * 8 + 4] += bf16_lo(bv.z); x[j * 8 + 5] += bf16_hi(bv.z); x[j * 8 + 6] += bf16_lo(bv.w); x[j * 8 + 7] += bf16_hi(bv.w);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 16; ++e) x[e] = __bfloat162float(__float2bfloat16_rn(x[e]));
+}
+
+__device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtensorMap* tm, uint32_t t_addr, int part,
+                                                  int head0, int n0, int heads_in_tile, int b, int l0, int r_local,
+                                                  bool rows_ok, uint8_t* out_stage, bool store_issuer) {
+  const __nv_bfloat16* w = part < 2 ? p.qk_scale[part] : nullptr;
+  const bool rotate = part < 2 && p.pe != nullptr && rows_ok;
+  float rstd[2] = {1.f, 1.f};
+  if (w != nullptr) {
+#pragma unroll 1
+    for (int hh = 0; hh < heads_in_tile; ++hh) {
+      float ss = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 16) {
+        float x[16];
+        qkv_load16(p, t_addr + hh * 128 + c, n0 + hh * 128 + c, x);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) ss += x[e] * x[e];
+      }
+      rstd[hh] = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+    }
+  }
+  const float4* pr = reinterpret_cast<const float4*>(p.pe) + static_cast<int64_t>(l0 + r_local) * 64;
+  // Eight steps of 16 columns; the pe entries of step s+1 are requested before step s is worked
+  // on, so that their latency hides behind it.
+  float4 f_next[8];
+  if (rotate) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f_next[i] = __ldg(pr + i);
+  }
+#pragma unroll
+  for (int s8 = 0; s8 < 8; ++s8) {
+    const int piece = s8 >> 2, step = s8 & 3;
+    const int c = s8 * 16;  // column within the head
+    if (step == 0) {
+      // both staging tiles must have been read out by the stores of the piece before
+      if (store_issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    float4 f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f_next[i];
+    if (rotate && s8 < 7) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f_next[i] = __ldg(pr + (c + 16) / 2 + i);
+    }
+#pragma unroll 1
+    for (int hh = 0; hh < heads_in_tile; ++hh) {
+      float x[16];
+      qkv_load16(p, t_addr + hh * 128 + c, n0 + hh * 128 + c, x);
+      if (w != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + c + j * 8));
+          const float r = rstd[hh];
+          x[j * 8 + 0] *= r * bf16_lo(wv.x); x[j * 8 + 1] *= r * bf16_hi(wv.x);
+          x[j * 8 + 2] *= r * bf16_lo(wv.y); x[j * 8 + 3] *= r * bf16_hi(wv.y);
+          x[j * 8 + 4] *= r * bf16_lo(wv.z); x[j * 8 + 5] *= r * bf16_hi(wv.z);
+          x[j * 8 + 6] *= r * bf16_lo(wv.w); x[j * 8 + 7] *= r * bf16_hi(wv.w);
+        }
+      }
+      if (rotate) {
+        // pe[l, i] = {f00, f01, f10, f11}: out[2i] = f00 x[2i] + f01 x[2i+1], out[2i+1] = f10 x[2i] + f11 x[2i+1]
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float a0 = x[2 * i], a1 = x[2 * i + 1];
+          x[2 * i] = f[i].x * a0 + f[i].y * a1;
+          x[2 * i + 1] = f[i].z * a0 + f[i].w * a1;
+        }
+      }
+      uint8_t* line = out_stage + hh * OUT_BUF_BYTES + r_local * 128;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const float* v = &x[jj * 8];
+        uint4 o;
+        o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
+        o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+        *reinterpret_cast<uint4*>(line + (((step * 2 + jj) ^ (r_local & 7)) << 4)) = o;
+      }
+    }
+    if (step == 3) {
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (store_issuer && rows_ok) {
+        for (int hh = 0; hh < heads_in_tile; ++hh)
+          asm volatile(
+              "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
+                  reinterpret_cast<uint64_t>(tm)),
+              "r"(smem_u32(out_stage + hh * OUT_BUF_BYTES)), "r"(piece * 64), "r"(l0), "r"(head0 + hh), "r"(b), "r"(part)
+              : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+  }
+}
+
+// kQkvHeads selects the epilogue at compile time, so that the ordinary kernel carries none of the
+// head epilogue's code or register pressure.
+template <bool kQkvHeads>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ Grouped g) {
   extern __shared__ uint8_t smem_raw[];
@@ -459,6 +589,17 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
       // The tile leaves in four 64-column pieces: registers -> swizzled staging tile in shared
       // memory -> one TMA store of full 128-byte lines.  (Storing 16 bytes per thread straight
       // to global memory, 32 different rows per warp instruction, cost 9 % of the GEMM.)
+      if constexpr (kQkvHeads) {
+        const int hd = p.heads * 128;
+        const int part = n0 / hd;
+        const int head0 = (n0 - part * hd) / 128;
+        const bool rows_ok = row0 < p.M;  // M is a multiple of 128 here: a CTA's rows exist or do not
+        const int b = row0 / (int)p.rows_per_batch;
+        const int l0 = p.row_offset + (row0 - b * (int)p.rows_per_batch);
+        const int heads_in_tile = (p.N - n0) >= BN ? BN / 128 : (p.N - n0) / 128;
+        qkv_tile_epilogue(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok, out_stage,
+                          store_issuer);
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / OUT_CHUNK_COLS; ++c) {
         if (n0 + c * OUT_CHUNK_COLS >= p.N) break;  // uniform
@@ -483,6 +624,7 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         ++out_chunks;
+      }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -574,6 +716,7 @@ static int prepare_problem(const fluxb_linear_problem& a, int64_t N, int64_t K, 
   p.tiles_n = (int)((N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.status = device_status_ptr();
+  p.pe = nullptr; p.qk_scale[0] = p.qk_scale[1] = nullptr; p.row_offset = 0; p.heads = 0; p.l_total = 0; p.eps = 0.f;
   p.pair_stages = fluxb::gemm2::STAGES;
   {
     // Keep the smaller operand resident in L2 when it fits, sweep the larger one.
@@ -652,14 +795,83 @@ extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int co
     ++g.count;
   }
   if (use_pair && g.count > 0) {
-    cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          fluxb::gemm2::SMEM_BYTES);
     if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
     const int pairs = g.total_tiles < sm_count() / 2 ? g.total_tiles : sm_count() / 2;
-    fluxb::gemm2::gemm_pair_kernel<<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
+    fluxb::gemm2::gemm_pair_kernel<false><<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: launch failed: %s", cudaGetErrorString(e));
+  return FLUXB_OK;
+}
+
+extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
+                                        int count, int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K,
+                                        void* qkv_out, float eps, fluxb_stream_t stream) {
+  using namespace fluxb::gemm;
+  if (count < 1 || count > fluxb::gemm2::MAX_PROBLEMS || !problems || !streams)
+    return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: 1..%d problems with their stream descriptions", fluxb::gemm2::MAX_PROBLEMS);
+  if (!use_pair_kernel()) return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: needs the CTA-pair kernel (FLUXB_GEMM_PAIR=0 is set)");
+  if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: head_dim %lld (only 128)", (long long)D);
+  if (B <= 0 || H <= 0 || L_total <= 0 || K <= 0 || B > 65535 || H > 65535 || L_total > (1 << 30))
+    return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: bad sizes");
+  if (!qkv_out || !aligned16(qkv_out)) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: output null or misaligned");
+  const int64_t N = 3 * H * D;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  fluxb::gemm2::Grouped g;
+  g.count = 0;
+  g.total_tiles = 0;
+  g.pair_stages = fluxb::gemm2::STAGES;
+  // one 5-D map over [3, B, H, L_total, D] for all problems
+  CUtensorMap tm_out;
+  {
+    const uint64_t dims[5] = {(uint64_t)D, (uint64_t)L_total, (uint64_t)H, (uint64_t)B, 3};
+    const uint64_t strides[4] = {(uint64_t)D * 2, (uint64_t)L_total * D * 2, (uint64_t)H * L_total * D * 2,
+                                 (uint64_t)B * H * L_total * D * 2};
+    const uint32_t box[5] = {fluxb::gemm2::OUT_CHUNK_COLS, fluxb::gemm2::BM, 1, 1, 1};
+    int rc = encode_tmap_bf16(&tm_out, qkv_out, 5, dims, strides, box);
+    if (rc != FLUXB_OK) return rc;
+  }
+  for (int i = 0; i < count; ++i) {
+    fluxb_linear_problem a = problems[i];
+    const fluxb_qkv_stream& sdesc = streams[i];
+    const int64_t Ls = a.rows_per_batch;
+    if (a.M <= 0 || Ls <= 0 || a.M != B * Ls || Ls % 128)
+      return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: each stream needs M = B * rows_per_batch with rows_per_batch a multiple of 128");
+    if (sdesc.row_offset < 0 || sdesc.row_offset % 128 || sdesc.row_offset + Ls > L_total)
+      return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: row_offset must be a multiple of 128 inside the joint sequence");
+    if ((sdesc.q_scale == nullptr) != (sdesc.k_scale == nullptr) || !aligned16(sdesc.q_scale) || !aligned16(sdesc.k_scale) ||
+        !aligned16(sdesc.pe))
+      return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: scales go together; scales and pe must be 16-byte aligned");
+    a.y = qkv_out; a.ldy = D;  // only the 5-D map is used for the output
+    a.y2 = nullptr; a.resid = nullptr; a.gate = nullptr;
+    fluxb::gemm2::Problem& pr = g.prob[g.count];
+    int rc = prepare_problem(a, N, K, FLUXB_EPI_NONE, N, FLUXB_EPI_NONE, 0, true, &pr.tm_a, &pr.tm_b, &pr.p);
+    if (rc != FLUXB_OK) return rc;
+    pr.p.epi = EPI_QKV_HEADS;
+    pr.p.rows_per_batch = Ls;
+    pr.p.pe = sdesc.pe;
+    pr.p.qk_scale[0] = static_cast<const __nv_bfloat16*>(sdesc.q_scale);
+    pr.p.qk_scale[1] = static_cast<const __nv_bfloat16*>(sdesc.k_scale);
+    pr.p.row_offset = (int)sdesc.row_offset;
+    pr.p.heads = (int)H;
+    pr.p.l_total = (int)L_total;
+    pr.p.eps = eps;
+    pr.tm_y = tm_out;
+    pr.tm_y2 = tm_out;
+    pr.tiles_m = (int)((a.M + 255) / 256);
+    pr.tile_start = g.total_tiles;
+    g.total_tiles += pr.tiles_m * pr.p.tiles_n;
+    ++g.count;
+  }
+  cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       fluxb::gemm2::SMEM_BYTES);
+  if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear_qkv_grouped: cannot set shared memory size: %s", cudaGetErrorString(e));
+  const int pairs = g.total_tiles < sm_count() / 2 ? g.total_tiles : sm_count() / 2;
+  fluxb::gemm2::gemm_pair_kernel<true><<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear_qkv_grouped: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
 }
 

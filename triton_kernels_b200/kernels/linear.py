@@ -101,6 +101,58 @@ def linear_grouped_into(
             launch_probe.append((tuple(pr["x2d"].shape[0] for pr in chunk), N, K, ev0, ev1))
 
 
+def qkv_projection_supported(stream_lengths, head_dim: int) -> bool:
+    """Whether linear_qkv_grouped_into takes these streams (see its docstring)."""
+    import os
+
+    if os.environ.get("FLUXB_GEMM_PAIR", "1") == "0":  # the single-CTA kernel has no such epilogue
+        return False
+    return head_dim == 128 and 1 <= len(stream_lengths) <= 4 and all(L > 0 and L % 128 == 0 for L in stream_lengths)
+
+
+def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_out: torch.Tensor, eps: float = 1e-6) -> None:
+    """q|k|v projections of up to four token streams with the whole path to attention in the GEMM
+    epilogue (fluxb_linear_qkv_grouped): per-head RMS norm of q and k, rotation with `pe`,
+    head-major layout, streams concatenated in list order.
+
+    streams[i]: dict(x [B, L_i, K] contiguous, w [3*H*D, K], b or None, q_scale [D] or None,
+    k_scale [D] or None); every L_i a multiple of 128.  pe: fp32 [1, 1, L, D/2, 2, 2] over the joint
+    sequence or None.  qkv_out: bf16 [3, B, H, L, D] contiguous with L = sum L_i, D = 128."""
+    three, B, H, L, D = qkv_out.shape
+    assert three == 3 and qkv_out.is_contiguous() and qkv_out.dtype == torch.bfloat16
+    assert sum(s["x"].shape[1] for s in streams) == L
+    pe_c = None
+    if pe is not None:
+        pe_c = pe if (pe.dtype == torch.float32 and pe.is_contiguous()) else pe.to(torch.float32).contiguous()
+    K = streams[0]["w"].shape[1]
+    arr = (_lib.LinearProblem * len(streams))()
+    desc = (_lib.QkvStream * len(streams))()
+    keep = []
+    row = 0
+    for slot, d, st in zip(arr, desc, streams):
+        x, w = st["x"], st["w"]
+        assert x.is_contiguous() and x.shape[0] == B and x.shape[2] == K and tuple(w.shape) == (3 * H * D, K) and w.stride(1) == 1
+        qs, ks = st.get("q_scale"), st.get("k_scale")
+        if qs is not None:
+            qs, ks = qs.to(torch.bfloat16), ks.to(torch.bfloat16)
+            keep += [qs, ks]
+        slot.x, slot.w, slot.bias, slot.y = _lib.ptr(x), _lib.ptr(w), _lib.ptr(st.get("b")), None
+        slot.M, slot.ldx, slot.ldw, slot.ldy = B * x.shape[1], K, w.stride(0), 0
+        slot.rows_per_batch = x.shape[1]
+        d.pe, d.q_scale, d.k_scale, d.row_offset = _lib.ptr(pe_c), _lib.ptr(qs), _lib.ptr(ks), row
+        row += x.shape[1]
+    if launch_probe is not None:
+        ev0 = torch.cuda.Event(enable_timing=True)
+        ev0.record()
+    _lib.check(
+        _lib.load().fluxb_linear_qkv_grouped(arr, desc, len(streams), B, H, D, L, K, _lib.ptr(qkv_out), eps, _lib.stream_handle())
+    )
+    if launch_probe is not None:
+        ev1 = torch.cuda.Event(enable_timing=True)
+        ev1.record()
+        launch_probe.append((tuple(B * st["x"].shape[1] for st in streams), 3 * H * D, K, ev0, ev1))
+
+
 def _as_2d(x: torch.Tensor, K: int) -> torch.Tensor:
     x2d = x.reshape(-1, K)
     if x2d.stride(1) != 1 or x2d.stride(0) % 8 or x2d.data_ptr() % 16:

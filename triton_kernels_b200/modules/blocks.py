@@ -21,6 +21,7 @@ difference is far below bf16 resolution).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -28,7 +29,13 @@ from torch import Tensor, nn
 
 from triton_kernels_b200 import _lib
 from triton_kernels_b200.kernels.attention import attention_into, attention_scatter_into, scaled_dot_product_attention
-from triton_kernels_b200.kernels.linear import linear, linear_grouped_into, linear_into
+from triton_kernels_b200.kernels.linear import (
+    linear,
+    linear_grouped_into,
+    linear_into,
+    linear_qkv_grouped_into,
+    qkv_projection_supported,
+)
 from triton_kernels_b200.kernels.normalization import layer_norm_modulation_into
 from triton_kernels_b200.kernels.positional_embedding import apply_rope
 from triton_kernels_b200.modules.normalization import QKNorm
@@ -265,6 +272,8 @@ class DoubleStreamBlock(nn.Module):
         self.txt_attn = SelfAttention(dim=hidden_size, num_heads=num_heads, qkv_bias=qkv_bias)
         self.txt_mlp = MLP(hidden_size, mlp_hidden_dim)
         self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
+        # QK norm + RoPE + head-major layout in the qkv GEMM's epilogue when shapes allow (FLUXB_FUSE_QKV=0: off)
+        self.fuse_qkv_epilogue = os.environ.get("FLUXB_FUSE_QKV", "1") != "0"
         self._side_stream = None  # created on first use
 
     def forward(self, img: Tensor, txt: Tensor, vec: Tensor, pe: Tensor,
@@ -305,15 +314,25 @@ class DoubleStreamBlock(nn.Module):
             g = mod[:, chunk * C : (chunk + 1) * C]
             return (g, g.stride(0) if B > 1 else 0) if b is None else (g[b : b + 1], 0)
 
-        # both streams' qkv projections in one launch
         h1 = [h_txt, h_img]
-        qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]
-        linear_grouped_into([
-            dict(x2d=h.view(B * L, C), w=a.qkv.weight, b=a.qkv.bias, y=o.view(B * L, 3 * C))
-            for h, a, o, L in zip(h1, attns, qkvs, Ls)])
-
-        attn = _joint_attention([(qkvs[0], self.txt_attn.norm), (qkvs[1], self.img_attn.norm)], pe, H, D**-0.5,
-                                None, self.sequence_parallel)
+        sp = self.sequence_parallel
+        if (sp is None or sp.world == 1) and self.fuse_qkv_epilogue and qkv_projection_supported(Ls, D):
+            # both streams' qkv projections in one launch whose epilogue also does the QK norm, the
+            # rotation and the head-major text|image layout attention reads
+            qkv_heads = torch.empty((3, B, H, Lt + Li, D), device=dev, dtype=dt)
+            linear_qkv_grouped_into([
+                dict(x=h, w=a.qkv.weight, b=a.qkv.bias, q_scale=a.norm.query_norm.scale, k_scale=a.norm.key_norm.scale)
+                for h, a in zip(h1, attns)], pe, qkv_heads, eps=1e-6)
+            attn = torch.empty((B, Lt + Li, C), device=dev, dtype=dt)
+            attention_into(qkv_heads[0], qkv_heads[1], qkv_heads[2], attn.unflatten(2, (H, D)).permute(0, 2, 1, 3), D**-0.5)
+        else:
+            # both streams' qkv projections in one launch, then the assembly kernel
+            qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]
+            linear_grouped_into([
+                dict(x2d=h.view(B * L, C), w=a.qkv.weight, b=a.qkv.bias, y=o.view(B * L, 3 * C))
+                for h, a, o, L in zip(h1, attns, qkvs, Ls)])
+            attn = _joint_attention([(qkvs[0], self.txt_attn.norm), (qkvs[1], self.img_attn.norm)], pe, H, D**-0.5,
+                                    None, sp)
 
         # proj + gate/residual: the rows of one stream of one batch item are one strided 2-D block
         x1 = [torch.empty_like(x) for x in xs]
