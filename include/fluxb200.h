@@ -240,6 +240,10 @@ int fluxb_silu(const void* x, void* out, int64_t n, int dtype, fluxb_stream_t st
  *                multiple of 128).
  *   qkv_out: bf16 [3, B, H, L_total, D].  D must be 128.  The projection is rounded to bf16
  *   before the norm, as the reference's bf16 Linear output is.
+ *   N2 > 0: w has N2 more rows after the 3*H*D of q|k|v (bias likewise); those columns are an
+ *   ordinary output, written to problems[i].y2 (row stride ldy2) with epilogue epi2 (none or
+ *   GELU, round_before_act as in fluxb_linear).  This is linear1 of the single-stream block
+ *   (triton_kernels/modules/blocks.py:93,108-110): qkv and the MLP's up-projection in one GEMM.
  */
 typedef struct {
   const float* pe;
@@ -249,7 +253,7 @@ typedef struct {
 } fluxb_qkv_stream;
 int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams, int count,
                              int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K, void* qkv_out,
-                             float eps, fluxb_stream_t stream);
+                             float eps, int64_t N2, int epi2, int round_before_act, fluxb_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Sequence-parallel (Ulysses) exchange over peer memory.  The reference has no multi-GPU path,

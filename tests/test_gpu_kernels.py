@@ -407,3 +407,24 @@ def test_double_block_fused_qkv_epilogue_matches_unfused(tk):
     for a, b in ((a_img, b_img), (a_txt, b_txt)):
         rel = float((a.float() - b.float()).norm() / b.float().norm())
         assert rel < 3e-3, rel
+
+
+def test_single_block_fused_qkv_epilogue_matches_unfused(tk):
+    g = gen(63)
+    C, H, L = 512, 4, 384
+    blk = tk.SingleStreamBlock(C, H, 4.0).to(BF).cuda()
+    with torch.no_grad():
+        for name, p in blk.named_parameters():
+            p.copy_((torch.randn(p.shape, generator=g) * (0.1 if name.endswith("scale") else 0.03)
+                     + (1.0 if name.endswith("scale") else 0.0)).to(BF))
+    x = torch.randn(2, L, C, generator=g).to(BF).cuda()
+    vec = torch.randn(2, C, generator=g).to(BF).cuda()
+    pe = torch.randn(1, 1, L, C // H // 2, 2, 2, generator=g).cuda()
+    with torch.no_grad():
+        blk.fuse_qkv_epilogue = True
+        a = blk(x, vec, pe)
+        blk.fuse_qkv_epilogue = False
+        b = blk(x, vec, pe)
+    torch.cuda.synchronize()
+    rel = float((a.float() - b.float()).norm() / b.float().norm())
+    assert rel < 3e-3, rel

@@ -589,14 +589,14 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
       // The tile leaves in four 64-column pieces: registers -> swizzled staging tile in shared
       // memory -> one TMA store of full 128-byte lines.  (Storing 16 bytes per thread straight
       // to global memory, 32 different rows per warp instruction, cost 9 % of the GEMM.)
-      if constexpr (kQkvHeads) {
+      if (kQkvHeads && !second) {
         const int hd = p.heads * 128;
         const int part = n0 / hd;
         const int head0 = (n0 - part * hd) / 128;
         const bool rows_ok = row0 < p.M;  // M is a multiple of 128 here: a CTA's rows exist or do not
         const int b = row0 / (int)p.rows_per_batch;
         const int l0 = p.row_offset + (row0 - b * (int)p.rows_per_batch);
-        const int heads_in_tile = (p.N - n0) >= BN ? BN / 128 : (p.N - n0) / 128;
+        const int heads_in_tile = (p.split - n0) >= BN ? BN / 128 : (p.split - n0) / 128;  // split = 3*heads*128
         qkv_tile_epilogue(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok, out_stage,
                           store_issuer);
       } else {
@@ -608,8 +608,12 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
         tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS + 32, r1);
         tmem_wait_ld();
         uint8_t* buf = out_stage + (out_chunks & 1) * OUT_BUF_BYTES;
-        // the store issued from this staging tile two pieces ago must have read it out
-        if (store_issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        // the store issued from this staging tile two pieces ago must have read it out (after a
+        // head-epilogue tile, whose last stores read both staging tiles: all of them)
+        if (store_issuer) {
+          if (kQkvHeads && c == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         uint8_t* line = buf + r_local * 128;
         epilogue_chunk(p, r0, row, n0 + c * OUT_CHUNK_COLS, second, line, 0, r_local & 7);
@@ -808,7 +812,8 @@ extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int co
 
 extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
                                         int count, int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K,
-                                        void* qkv_out, float eps, fluxb_stream_t stream) {
+                                        void* qkv_out, float eps, int64_t N2, int epi2, int round_before_act,
+                                        fluxb_stream_t stream) {
   using namespace fluxb::gemm;
   if (count < 1 || count > fluxb::gemm2::MAX_PROBLEMS || !problems || !streams)
     return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: 1..%d problems with their stream descriptions", fluxb::gemm2::MAX_PROBLEMS);
@@ -817,7 +822,11 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
   if (B <= 0 || H <= 0 || L_total <= 0 || K <= 0 || B > 65535 || H > 65535 || L_total > (1 << 30))
     return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: bad sizes");
   if (!qkv_out || !aligned16(qkv_out)) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: output null or misaligned");
-  const int64_t N = 3 * H * D;
+  if (N2 < 0 || N2 % 8) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: N2 must be a non-negative multiple of 8");
+  if (epi2 != FLUXB_EPI_NONE && epi2 != FLUXB_EPI_GELU)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: the extra columns take no epilogue or GELU");
+  const int64_t N_qkv = 3 * H * D;
+  const int64_t N = N_qkv + N2;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   fluxb::gemm2::Grouped g;
   g.count = 0;
@@ -844,10 +853,11 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     if ((sdesc.q_scale == nullptr) != (sdesc.k_scale == nullptr) || !aligned16(sdesc.q_scale) || !aligned16(sdesc.k_scale) ||
         !aligned16(sdesc.pe))
       return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: scales go together; scales and pe must be 16-byte aligned");
-    a.y = qkv_out; a.ldy = D;  // only the 5-D map is used for the output
-    a.y2 = nullptr; a.resid = nullptr; a.gate = nullptr;
+    a.y = qkv_out; a.ldy = D;  // the q|k|v columns leave through the 5-D map only
+    a.resid = nullptr; a.gate = nullptr;
+    if (N2 == 0) a.y2 = nullptr;
     fluxb::gemm2::Problem& pr = g.prob[g.count];
-    int rc = prepare_problem(a, N, K, FLUXB_EPI_NONE, N, FLUXB_EPI_NONE, 0, true, &pr.tm_a, &pr.tm_b, &pr.p);
+    int rc = prepare_problem(a, N, K, FLUXB_EPI_NONE, N_qkv, epi2, round_before_act, true, &pr.tm_a, &pr.tm_b, &pr.p);
     if (rc != FLUXB_OK) return rc;
     pr.p.epi = EPI_QKV_HEADS;
     pr.p.rows_per_batch = Ls;
@@ -860,6 +870,13 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     pr.p.eps = eps;
     pr.tm_y = tm_out;
     pr.tm_y2 = tm_out;
+    if (N2 > 0) {  // extra columns [3*H*D, 3*H*D + N2): an ordinary output with epilogue epi2
+      const uint32_t box[2] = {fluxb::gemm2::OUT_CHUNK_COLS, fluxb::gemm2::BM};
+      const uint64_t dims2[2] = {(uint64_t)N2, (uint64_t)a.M};
+      const uint64_t strides2[1] = {(uint64_t)a.ldy2 * 2};
+      rc = encode_tmap_bf16(&pr.tm_y2, a.y2, 2, dims2, strides2, box);
+      if (rc != FLUXB_OK) return rc;
+    }
     pr.tiles_m = (int)((a.M + 255) / 256);
     pr.tile_start = g.total_tiles;
     g.total_tiles += pr.tiles_m * pr.p.tiles_n;

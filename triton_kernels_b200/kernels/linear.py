@@ -110,14 +110,17 @@ def qkv_projection_supported(stream_lengths, head_dim: int) -> bool:
     return head_dim == 128 and 1 <= len(stream_lengths) <= 4 and all(L > 0 and L % 128 == 0 for L in stream_lengths)
 
 
-def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_out: torch.Tensor, eps: float = 1e-6) -> None:
+def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_out: torch.Tensor, eps: float = 1e-6,
+                            epi2: int = _lib.EPI_NONE, round_before_act: bool = False) -> None:
     """q|k|v projections of up to four token streams with the whole path to attention in the GEMM
     epilogue (fluxb_linear_qkv_grouped): per-head RMS norm of q and k, rotation with `pe`,
     head-major layout, streams concatenated in list order.
 
     streams[i]: dict(x [B, L_i, K] contiguous, w [3*H*D, K], b or None, q_scale [D] or None,
     k_scale [D] or None); every L_i a multiple of 128.  pe: fp32 [1, 1, L, D/2, 2, 2] over the joint
-    sequence or None.  qkv_out: bf16 [3, B, H, L, D] contiguous with L = sum L_i, D = 128."""
+    sequence or None.  qkv_out: bf16 [3, B, H, L, D] contiguous with L = sum L_i, D = 128.
+    A stream may carry `y2` ([B*L_i, N2] view, unit column stride): then w (and b) have N2 more rows
+    after the q|k|v ones and those columns go to y2 with epilogue `epi2` (none or GELU)."""
     three, B, H, L, D = qkv_out.shape
     assert three == 3 and qkv_out.is_contiguous() and qkv_out.dtype == torch.bfloat16
     assert sum(s["x"].shape[1] for s in streams) == L
@@ -125,13 +128,18 @@ def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_ou
     if pe is not None:
         pe_c = pe if (pe.dtype == torch.float32 and pe.is_contiguous()) else pe.to(torch.float32).contiguous()
     K = streams[0]["w"].shape[1]
+    N2 = streams[0]["y2"].shape[1] if streams[0].get("y2") is not None else 0
     arr = (_lib.LinearProblem * len(streams))()
     desc = (_lib.QkvStream * len(streams))()
     keep = []
     row = 0
     for slot, d, st in zip(arr, desc, streams):
         x, w = st["x"], st["w"]
-        assert x.is_contiguous() and x.shape[0] == B and x.shape[2] == K and tuple(w.shape) == (3 * H * D, K) and w.stride(1) == 1
+        y2 = st.get("y2")
+        n2 = y2.shape[1] if y2 is not None else 0
+        assert x.is_contiguous() and x.shape[0] == B and x.shape[2] == K and tuple(w.shape) == (3 * H * D + n2, K) and w.stride(1) == 1
+        assert n2 == N2
+        slot.y2, slot.ldy2 = _lib.ptr(y2), (y2.stride(0) if y2 is not None else 0)
         qs, ks = st.get("q_scale"), st.get("k_scale")
         if qs is not None:
             qs, ks = qs.to(torch.bfloat16), ks.to(torch.bfloat16)
@@ -145,12 +153,13 @@ def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_ou
         ev0 = torch.cuda.Event(enable_timing=True)
         ev0.record()
     _lib.check(
-        _lib.load().fluxb_linear_qkv_grouped(arr, desc, len(streams), B, H, D, L, K, _lib.ptr(qkv_out), eps, _lib.stream_handle())
+        _lib.load().fluxb_linear_qkv_grouped(arr, desc, len(streams), B, H, D, L, K, _lib.ptr(qkv_out), eps, N2, epi2,
+                                             int(round_before_act), _lib.stream_handle())
     )
     if launch_probe is not None:
         ev1 = torch.cuda.Event(enable_timing=True)
         ev1.record()
-        launch_probe.append((tuple(B * st["x"].shape[1] for st in streams), 3 * H * D, K, ev0, ev1))
+        launch_probe.append((tuple(B * st["x"].shape[1] for st in streams), 3 * H * D + N2, K, ev0, ev1))
 
 
 def _as_2d(x: torch.Tensor, K: int) -> torch.Tensor:

@@ -224,6 +224,8 @@ class SingleStreamBlock(nn.Module):
         self.mlp_act = nn.GELU(approximate="tanh")
         self.modulation = Modulation(hidden_size, double=False)
         self.sequence_parallel = None  # set to a parallel.SequenceParallel to shard tokens over ranks
+        # QK norm + RoPE + head-major layout in linear1's epilogue when shapes allow (FLUXB_FUSE_QKV=0: off)
+        self.fuse_qkv_epilogue = os.environ.get("FLUXB_FUSE_QKV", "1") != "0"
 
     def forward(self, x: Tensor, vec: Tensor, pe: Tensor, modulation: Tensor | None = None) -> Tensor:
         """`modulation` may carry the packed [B, 3C] output of `self.modulation.packed(vec)`
@@ -237,8 +239,23 @@ class SingleStreamBlock(nn.Module):
         x_mod = _ln_mod(x, mod, 0)
 
         # linear1: columns [0, 3C) -> qkv, columns [3C, 3C+M) -> GELU -> cat[:, :, C:]
-        qkv = torch.empty((B, L, 3 * C), device=x.device, dtype=x.dtype)
         cat = torch.empty((B, L, C + M), device=x.device, dtype=x.dtype)  # attn | gelu(mlp)
+        sp = self.sequence_parallel
+        if ((sp is None or sp.world == 1) and self.fuse_qkv_epilogue and qkv_projection_supported((L,), D)
+                and (3 * C) % 256 == 0 and M % 8 == 0):
+            # one GEMM: the q|k|v columns leave normalised, rotated and head-major, the MLP columns
+            # through GELU into the concat buffer
+            qkv_heads = torch.empty((3, B, H, L, D), device=x.device, dtype=x.dtype)
+            linear_qkv_grouped_into(
+                [dict(x=x_mod, w=self.linear1.weight, b=self.linear1.bias, q_scale=self.norm.query_norm.scale,
+                      k_scale=self.norm.key_norm.scale, y2=cat.view(B * L, C + M)[:, C:])],
+                pe, qkv_heads, eps=1e-6, epi2=_lib.EPI_GELU)
+            attention_into(qkv_heads[0], qkv_heads[1], qkv_heads[2],
+                           cat[:, :, :C].unflatten(2, (H, D)).permute(0, 2, 1, 3), self.scale)
+            out = torch.empty_like(x)
+            _gated_linear(cat.view(B * L, C + M), self.linear2, x.view(B * L, C), mod[:, 2 * C : 3 * C], L, out.view(B * L, C))
+            return out
+        qkv = torch.empty((B, L, 3 * C), device=x.device, dtype=x.dtype)
         if (3 * C) % 256 == 0:
             linear_into(
                 x_mod.view(B * L, C), self.linear1.weight, self.linear1.bias, qkv.view(B * L, 3 * C),
