@@ -319,6 +319,17 @@ def run_micro(which: str, steps: int, warmup: int):
                 for _ in range(2)]
         calls = [lambda x=x, w=w, b=b, y=y: linear_into(x, w, b, y, epi=_lib.EPI_GELU) for x, w, b, y in bufs]
         emit("linear_bias_gelu[M4608,K3072,N12288]", time_calls(calls), 2.0 * M * N * K, "tensor")
+    if want("linear_qkv"):
+        # both streams' q|k|v projection with QK norm, RoPE and the head-major layout in the epilogue
+        from triton_kernels_b200.kernels.linear import linear_qkv_grouped_into
+        Lt_, Li_ = 512, L - 512
+        ones = torch.ones(D, device=dev, dtype=BF)
+        pe6 = pe.view(1, 1, L, D // 2, 2, 2)
+        bufs = [([randn(1, Lt_, Cc), randn(1, Li_, Cc)], [randn(3 * Cc, Cc, std=0.02) for _ in range(2)],
+                 torch.empty(3, 1, Hh, L, D, device=dev, dtype=BF)) for _ in range(2)]
+        calls = [lambda xs=xs, ws=ws, o=o: linear_qkv_grouped_into(
+            [dict(x=x, w=w, b=None, q_scale=ones, k_scale=ones) for x, w in zip(xs, ws)], pe6, o) for xs, ws, o in bufs]
+        emit("linear_qkv_heads[M512+4096,K3072,N9216]", time_calls(calls), 2.0 * L * 3 * Cc * Cc, "tensor")
     if want("attention"):
         bufs = [tuple(randn(1, Hh, L, D) for _ in range(3)) + (torch.empty(1, L, Hh, D, device=dev, dtype=BF),)
                 for _ in range(3)]
@@ -598,7 +609,7 @@ def main():
     ap.add_argument("--sweep", default=None, help="sequence-length sweep with the reference benchmark scripts' shapes: "
                     "all | linear | attention | layer_norm | rms_norm | rope (--steps = timed calls per point)")
     ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")
-    ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | layer_norm_modulation | rms_norm | "
+    ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | linear_qkv | layer_norm_modulation | rms_norm | "
                     "rope | qkv_prepare | modulation_projection | linear_gelu | attention")
     args = ap.parse_args()
     if args.micro:
