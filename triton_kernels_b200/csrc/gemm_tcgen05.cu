@@ -300,7 +300,7 @@ constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int OUT_CHUNK_COLS = 64;                       // output columns per staged TMA store
 constexpr int OUT_BUF_BYTES = BM * OUT_CHUNK_COLS * 2;   // 128 rows x 128 bytes
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // TMA warp, MMA warp, two groups of four epilogue warps
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BUF_BYTES + 1024 + 256;
 constexpr int MAX_PROBLEMS = 4;
@@ -450,9 +450,11 @@ __device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtenso
   }
 }
 
-// kQkvHeads selects the epilogue at compile time, so that the ordinary kernel carries none of the
-// head epilogue's code or register pressure.
-template <bool kQkvHeads>
+// kMode selects the epilogue at compile time, so that the ordinary kernel carries none of the other
+// forms' code or register pressure:
+//   0  ordinary (bias / GELU / gate+residual / column split)
+//   1  q|k|v columns through the head epilogue, columns from `split` on ordinary
+template <int kMode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ Grouped g) {
   extern __shared__ uint8_t smem_raw[];
@@ -482,7 +484,7 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);
+      mbar_init(&acc_empty[a], 16);  // one arrival per epilogue warp of both CTAs
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -563,11 +565,19 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
     }
     __syncwarp();
   } else {
+    // Two groups of four epilogue warps (warps 2-5 and 6-9; warp w reads TMEM lane quadrant w % 4).
+    // A tile leaves in four 64-column pieces; group eg takes pieces eg and eg + 2 with a staging
+    // tile, a named barrier and a store-issuing thread of its own.  One warp per scheduler was
+    // not enough to cover the latencies inside a piece (accumulator load, bias / gate / residual
+    // loads, GELU): measured per tile and CTA, 20 000 cycles for the plain epilogue, 28 000 with
+    // GELU and 37 000 with gate + residual, against a main loop of 24 600 cycles at K = 3072.
     const int quad = warp & 3;
+    const int eg = (warp - 2) >> 2;
+    const int bar_id = 1 + eg;
     int local = 0;
     bool ok = true;
     const uint32_t acc_empty_leader0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
-    const bool store_issuer = warp == 2 && lane == 0;
+    const bool store_issuer = warp == 2 + 4 * eg && lane == 0;
     uint32_t out_chunks = 0;
     for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
       const Problem& pr = g.prob[find_problem(g, tile)];
@@ -576,20 +586,22 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
       tile_coords(p, tile - pr.tile_start, pr.tiles_m, m_blk, n_blk);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      if (!mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, status, 45)) { ok = false; break; }
-      tc_fence_after_sync();
       const int row0 = m_blk * 2 * BM + (int)rank * BM;
       const int r_local = quad * 32 + lane;
       const int row = row0 + r_local;
       const int n0 = n_blk * BN;
       const bool second = n0 >= p.split;
+      if (!mbar_wait_cluster(&acc_full[acc], acc_phase, abort_flag, status, 45)) { ok = false; break; }
+      tc_fence_after_sync();
       const CUtensorMap* tm_out = second ? &pr.tm_y2 : &pr.tm_y;
       const int out_col0 = second ? n0 - p.split : n0;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       // The tile leaves in four 64-column pieces: registers -> swizzled staging tile in shared
       // memory -> one TMA store of full 128-byte lines.  (Storing 16 bytes per thread straight
       // to global memory, 32 different rows per warp instruction, cost 9 % of the GEMM.)
-      if (kQkvHeads && !second) {
+      if (kMode == 1 && eg == 1) {
+        // the head epilogue and its ordinary tail columns are worked by group 0 alone
+      } else if (kMode == 1 && !second) {
         const int hd = p.heads * 128;
         const int part = n0 / hd;
         const int head0 = (n0 - part * hd) / 128;
@@ -599,7 +611,8 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
         const int heads_in_tile = (p.split - n0) >= BN ? BN / 128 : (p.split - n0) / 128;  // split = 3*heads*128
         qkv_tile_epilogue(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok, out_stage,
                           store_issuer);
-      } else {
+      } else if constexpr (kMode == 1) {
+      // ordinary columns behind the q|k|v ones (group 0 alone, both staging tiles in turn)
 #pragma unroll 1
       for (int c = 0; c < BN / OUT_CHUNK_COLS; ++c) {
         if (n0 + c * OUT_CHUNK_COLS >= p.N) break;  // uniform
@@ -611,7 +624,7 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
         // the store issued from this staging tile two pieces ago must have read it out (after a
         // head-epilogue tile, whose last stores read both staging tiles: all of them)
         if (store_issuer) {
-          if (kQkvHeads && c == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          if (c == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -628,6 +641,34 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
         ++out_chunks;
+      }
+      } else {
+      // kMode 0: this group's two pieces, through its own staging tile
+      uint8_t* buf = out_stage + eg * OUT_BUF_BYTES;
+      uint8_t* line = buf + r_local * 128;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int c = eg + 2 * i;
+        if (n0 + c * OUT_CHUNK_COLS < p.N) {  // uniform
+          uint32_t r0[32], r1[32];
+          tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS, r0);
+          tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS + 32, r1);
+          tmem_wait_ld();
+          // this group's previous store must have read the staging tile out
+          if (store_issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+          epilogue_chunk(p, r0, row, n0 + c * OUT_CHUNK_COLS, second, line, 0, r_local & 7);
+          epilogue_chunk(p, r1, row, n0 + c * OUT_CHUNK_COLS + 32, second, line, 4, r_local & 7);
+          fence_proxy_async_smem();
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+          if (store_issuer) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(tm_out)),
+                         "r"(smem_u32(buf)), "r"(out_col0 + c * OUT_CHUNK_COLS), "r"(row0)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
       }
       }
       tc_fence_before_sync();
@@ -799,11 +840,11 @@ extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int co
     ++g.count;
   }
   if (use_pair && g.count > 0) {
-    cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         fluxb::gemm2::SMEM_BYTES);
+    auto kern = fluxb::gemm2::gemm_pair_kernel<0>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fluxb::gemm2::SMEM_BYTES);
     if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: cannot set shared memory size: %s", cudaGetErrorString(e));
     const int pairs = g.total_tiles < sm_count() / 2 ? g.total_tiles : sm_count() / 2;
-    fluxb::gemm2::gemm_pair_kernel<false><<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
+    kern<<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear: launch failed: %s", cudaGetErrorString(e));
@@ -882,11 +923,11 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     g.total_tiles += pr.tiles_m * pr.p.tiles_n;
     ++g.count;
   }
-  cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        fluxb::gemm2::SMEM_BYTES);
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear_qkv_grouped: cannot set shared memory size: %s", cudaGetErrorString(e));
   const int pairs = g.total_tiles < sm_count() / 2 ? g.total_tiles : sm_count() / 2;
-  fluxb::gemm2::gemm_pair_kernel<true><<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
+  fluxb::gemm2::gemm_pair_kernel<1><<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear_qkv_grouped: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
