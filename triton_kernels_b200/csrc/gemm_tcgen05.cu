@@ -334,10 +334,12 @@ __device__ __forceinline__ int find_problem(const Grouped& g, int tile) {
 // Epilogue of one 128-row x 256-column tile (two heads of q, of k or of v) for EPI_QKV_HEADS:
 // bias, rounding to bf16 (the projection's output precision in the reference), per-head RMS norm
 // and rotation for q and k in fp32 with one rounding at the end, head-major 5-D TMA stores at
-// (d, l, head, batch, part).  One thread owns one row.  The row's sum of squares is taken in a
-// first sweep over the accumulator; the second sweep goes 16 columns at a time for BOTH heads,
-// because the rotation entries depend on the row and the pair only: each batch of eight
-// pe entries is loaded once and used for the two heads.  Staging tile hh collects head hh.
+// (d, l, head, batch, part).  One thread of each epilogue group owns one row.  The row's sums of
+// squares are taken in a first sweep over the accumulator (by both groups); in the second sweep
+// a thread works 16 columns at a time for BOTH heads, because the rotation entries depend on
+// the row and the pair only: each batch of eight pe entries is loaded once and used for the
+// two heads.  The two groups take alternate 16-column steps; staging tile hh collects head hh
+// from both groups and is stored by group hh's issuing thread.
 __device__ __forceinline__ void qkv_load16(const Params& p, uint32_t taddr, int col, float (&x)[16]) {
   uint32_t r[16];
   tmem_ld_x16(taddr, r);
@@ -358,10 +360,10 @@ __device__ __forceinline__ void qkv_load16(const Params& p, uint32_t taddr, int 
 
 __device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtensorMap* tm, uint32_t t_addr, int part,
                                                   int head0, int n0, int heads_in_tile, int b, int l0, int r_local,
-                                                  bool rows_ok, uint8_t* out_stage, bool store_issuer) {
+                                                  bool rows_ok, uint8_t* out_stage, int eg, bool store_issuer) {
   const __nv_bfloat16* w = part < 2 ? p.qk_scale[part] : nullptr;
   const bool rotate = part < 2 && p.pe != nullptr && rows_ok;
-  float rstd[2] = {1.f, 1.f};
+  float rstd0 = 1.f, rstd1 = 1.f;
   if (w != nullptr) {
 #pragma unroll 1
     for (int hh = 0; hh < heads_in_tile; ++hh) {
@@ -373,42 +375,46 @@ __device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtenso
 #pragma unroll
         for (int e = 0; e < 16; ++e) ss += x[e] * x[e];
       }
-      rstd[hh] = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+      const float r = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+      if (hh == 0) rstd0 = r; else rstd1 = r;
     }
   }
   const float4* pr = reinterpret_cast<const float4*>(p.pe) + static_cast<int64_t>(l0 + r_local) * 64;
-  // Eight steps of 16 columns; the pe entries of step s+1 are requested before step s is worked
-  // on, so that their latency hides behind it.
+  // This group's four steps of 16 columns: steps eg and eg + 2 of each 64-column piece.  The pe
+  // entries of the next step are requested before the current one is worked on.
   float4 f_next[8];
   if (rotate) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f_next[i] = __ldg(pr + i);
+    for (int i = 0; i < 8; ++i) f_next[i] = __ldg(pr + (eg * 16) / 2 + i);
   }
 #pragma unroll
-  for (int s8 = 0; s8 < 8; ++s8) {
-    const int piece = s8 >> 2, step = s8 & 3;
-    const int c = s8 * 16;  // column within the head
-    if (step == 0) {
-      // both staging tiles must have been read out by the stores of the piece before
+  for (int it = 0; it < 4; ++it) {
+    const int piece = it >> 1;
+    const int step = eg + 2 * (it & 1);
+    const int c = piece * 64 + step * 16;  // column within the head
+    if ((it & 1) == 0) {
+      // both staging tiles must have been read out by the stores of the piece before (each
+      // issuer waits for its own), and nobody writes before both issuers are through
       if (store_issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 3, 256;" ::: "memory");
     }
     float4 f[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) f[i] = f_next[i];
-    if (rotate && s8 < 7) {
+    if (rotate && it < 3) {
+      const int cn = ((it + 1) >> 1) * 64 + (eg + 2 * ((it + 1) & 1)) * 16;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f_next[i] = __ldg(pr + (c + 16) / 2 + i);
+      for (int i = 0; i < 8; ++i) f_next[i] = __ldg(pr + cn / 2 + i);
     }
 #pragma unroll 1
     for (int hh = 0; hh < heads_in_tile; ++hh) {
       float x[16];
       qkv_load16(p, t_addr + hh * 128 + c, n0 + hh * 128 + c, x);
       if (w != nullptr) {
+        const float r = hh == 0 ? rstd0 : rstd1;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + c + j * 8));
-          const float r = rstd[hh];
           x[j * 8 + 0] *= r * bf16_lo(wv.x); x[j * 8 + 1] *= r * bf16_hi(wv.x);
           x[j * 8 + 2] *= r * bf16_lo(wv.y); x[j * 8 + 3] *= r * bf16_hi(wv.y);
           x[j * 8 + 4] *= r * bf16_lo(wv.z); x[j * 8 + 5] *= r * bf16_hi(wv.z);
@@ -434,16 +440,16 @@ __device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtenso
         *reinterpret_cast<uint4*>(line + (((step * 2 + jj) ^ (r_local & 7)) << 4)) = o;
       }
     }
-    if (step == 3) {
+    if ((it & 1) == 1) {
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (store_issuer && rows_ok) {
-        for (int hh = 0; hh < heads_in_tile; ++hh)
-          asm volatile(
-              "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
-                  reinterpret_cast<uint64_t>(tm)),
-              "r"(smem_u32(out_stage + hh * OUT_BUF_BYTES)), "r"(piece * 64), "r"(l0), "r"(head0 + hh), "r"(b), "r"(part)
-              : "memory");
+      asm volatile("bar.sync 3, 256;" ::: "memory");
+      // group eg's issuer stores staging tile eg = head eg of the tile
+      if (store_issuer && rows_ok && eg < heads_in_tile) {
+        asm volatile(
+            "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(
+                reinterpret_cast<uint64_t>(tm)),
+            "r"(smem_u32(out_stage + eg * OUT_BUF_BYTES)), "r"(piece * 64), "r"(l0), "r"(head0 + eg), "r"(b), "r"(part)
+            : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
@@ -578,7 +584,6 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
     bool ok = true;
     const uint32_t acc_empty_leader0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
     const bool store_issuer = warp == 2 + 4 * eg && lane == 0;
-    uint32_t out_chunks = 0;
     for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
       const Problem& pr = g.prob[find_problem(g, tile)];
       const Params& p = pr.p;
@@ -599,9 +604,7 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
       // The tile leaves in four 64-column pieces: registers -> swizzled staging tile in shared
       // memory -> one TMA store of full 128-byte lines.  (Storing 16 bytes per thread straight
       // to global memory, 32 different rows per warp instruction, cost 9 % of the GEMM.)
-      if (kMode == 1 && eg == 1) {
-        // the head epilogue and its ordinary tail columns are worked by group 0 alone
-      } else if (kMode == 1 && !second) {
+      if (kMode == 1 && !second) {
         const int hd = p.heads * 128;
         const int part = n0 / hd;
         const int head0 = (n0 - part * hd) / 128;
@@ -609,41 +612,10 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
         const int b = row0 / (int)p.rows_per_batch;
         const int l0 = p.row_offset + (row0 - b * (int)p.rows_per_batch);
         const int heads_in_tile = (p.split - n0) >= BN ? BN / 128 : (p.split - n0) / 128;  // split = 3*heads*128
-        qkv_tile_epilogue(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok, out_stage,
+        qkv_tile_epilogue(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok, out_stage, eg,
                           store_issuer);
-      } else if constexpr (kMode == 1) {
-      // ordinary columns behind the q|k|v ones (group 0 alone, both staging tiles in turn)
-#pragma unroll 1
-      for (int c = 0; c < BN / OUT_CHUNK_COLS; ++c) {
-        if (n0 + c * OUT_CHUNK_COLS >= p.N) break;  // uniform
-        uint32_t r0[32], r1[32];
-        tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS, r0);
-        tmem_ld_x32(t_addr + c * OUT_CHUNK_COLS + 32, r1);
-        tmem_wait_ld();
-        uint8_t* buf = out_stage + (out_chunks & 1) * OUT_BUF_BYTES;
-        // the store issued from this staging tile two pieces ago must have read it out (after a
-        // head-epilogue tile, whose last stores read both staging tiles: all of them)
-        if (store_issuer) {
-          if (c == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        uint8_t* line = buf + r_local * 128;
-        epilogue_chunk(p, r0, row, n0 + c * OUT_CHUNK_COLS, second, line, 0, r_local & 7);
-        epilogue_chunk(p, r1, row, n0 + c * OUT_CHUNK_COLS + 32, second, line, 4, r_local & 7);
-        fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (store_issuer) {
-          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                           reinterpret_cast<uint64_t>(tm_out)),
-                       "r"(smem_u32(buf)), "r"(out_col0 + c * OUT_CHUNK_COLS), "r"(row0)
-                       : "memory");
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-        ++out_chunks;
-      }
       } else {
-      // kMode 0: this group's two pieces, through its own staging tile
+      // ordinary columns: this group's two pieces, through its own staging tile
       uint8_t* buf = out_stage + eg * OUT_BUF_BYTES;
       uint8_t* line = buf + r_local * 128;
 #pragma unroll
