@@ -146,7 +146,7 @@ int fluxb_rms_norm(const void* x, const void* w, void* y, float* rstd, int64_t n
  * column sums (the caller reduces it over rows); dw_partial_rows is returned by
  * fluxb_rms_norm_bwd_partial_rows().
  */
-int fluxb_rms_norm_bwd_partial_rows(int64_t rows);
+int64_t fluxb_rms_norm_bwd_partial_rows(int64_t rows);
 int fluxb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                        float* dw_partial, int64_t rows, int64_t cols, int dtype,
                        fluxb_stream_t stream);

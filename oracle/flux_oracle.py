@@ -271,8 +271,10 @@ def last_layer(x: Tensor, vec: Tensor, params: dict, prefix: str = "final_layer.
 
 
 def sub_params(params: dict, prefix: str) -> dict:
+    # entries are read through params[k] so that a mapping which converts on access (the
+    # full-depth test keeps the weights in bf16 and upcasts one block at a time) works here too
     n = len(prefix)
-    return {k[n:]: v for k, v in params.items() if k.startswith(prefix)}
+    return {k[n:]: params[k] for k in params if k.startswith(prefix)}
 
 
 def flux_dit_forward(

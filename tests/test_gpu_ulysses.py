@@ -22,8 +22,12 @@ def _rank_main(rank: int, world: int, port: int, q_out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
 
+    import datetime
+
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short collective timeout: if the peer dies, this rank's next collective ends with an error
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from oracle import flux_oracle as O
         import triton_kernels_b200 as tk
@@ -68,15 +72,20 @@ def _rank_main(rank: int, world: int, port: int, q_out):
                     errs += [rel(got_img, want_img[:, rows_i]), rel(got_txt, want_txt[:, rows_t]),
                              rel(got_x[:, :Ltl], want_x[:, rows_t]), rel(got_x[:, Ltl:], want_x[:, Lt:][:, rows_i])]
                 torch.cuda.synchronize()
+                sp.check()  # raises if a flag wait of the peer exchange gave up
                 sp.close()
         code, where = _lib.device_status()
         assert code == 0, f"device status {code} at {where}"
         dist.barrier()
         q_out.put((rank, max(errs)))
     except Exception as e:  # noqa: BLE001
+        # The other rank may be blocked in a collective that this rank will never join: report and
+        # leave at once, without the collective teardown; the parent ends the peer.
         q_out.put((rank, repr(e)))
-    finally:
-        dist.destroy_process_group()
+        q_out.close()
+        q_out.join_thread()
+        os._exit(1)
+    dist.destroy_process_group()
 
 
 def test_sequence_parallel_blocks_match_single_gpu(lib):
@@ -91,9 +100,22 @@ def test_sequence_parallel_blocks_match_single_gpu(lib):
     procs = [ctx.Process(target=_rank_main, args=(r, world, port, q_out)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted(q_out.get(timeout=300) for _ in range(world))
-    for p in procs:
-        p.join(timeout=60)
+    results = []
+    try:
+        for _ in range(world):
+            results.append(q_out.get(timeout=300))
+            if not isinstance(results[-1][1], float):
+                break  # a rank failed: its peer may never finish
+    finally:
+        failed = len(results) < world or any(not isinstance(e, float) for _, e in results)
+        for p in procs:
+            p.join(timeout=5 if failed else 60)
+        for p in procs:  # no child may outlive the test holding a GPU
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=30)
+    results.sort()
+    assert len(results) == world or failed
     for rank, err in results:
         assert isinstance(err, float), f"rank {rank}: {err}"
         assert err < 5e-3, f"rank {rank}: sequence-parallel output differs from single-GPU output by {err}"

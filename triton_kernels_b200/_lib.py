@@ -50,7 +50,7 @@ SIGNATURES = {
     "fluxb_attention": (_I, [_P, _P, _P, _P] + [_L] * 5 + [_L] * 12 + [_F, _P]),
     "fluxb_layer_norm_modulation": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _F, _I, _P]),
     "fluxb_rms_norm": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P]),
-    "fluxb_rms_norm_bwd_partial_rows": (_I, [_L]),
+    "fluxb_rms_norm_bwd_partial_rows": (_L, [_L]),
     "fluxb_rms_norm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P]),
     "fluxb_rms_norm_bwd_static_max_floats": (_I, []),
     "fluxb_rms_norm_bwd_static": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _I, _P]),

@@ -464,8 +464,8 @@ static int attention_impl(const void* q, const void* k, const void* v, void* o, 
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   // V is consumed as the MN-major operand: 8-key groups are 1024 bytes apart (stride offset)
   // and the two 64-wide halves of head_dim are 16384 bytes apart (leading offset).
-  p.v_lbo = env_u32("FLUXB_ATTN_V_LBO", HALF_BYTES);
-  p.v_sbo = env_u32("FLUXB_ATTN_V_SBO", 1024);
+  p.v_lbo = HALF_BYTES;
+  p.v_sbo = 1024;
   p.status = device_status_ptr();
   p.rows_per_rank = n_ranks > 0 ? (int)rows_per_rank : 0;
   for (int i = 0; i < 8; ++i) p.o_rank[i] = i < n_ranks ? static_cast<__nv_bfloat16*>(o_bases[i]) : nullptr;

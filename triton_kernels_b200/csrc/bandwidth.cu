@@ -212,10 +212,12 @@ __device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, 
       : "memory");
 }
 
-// Waits (bounded) for this warp's row; returns false if it never arrived.
-__device__ __forceinline__ bool wait_row(uint64_t* bar) {
+// Waits (bounded) for this warp's row.  If the copy never lands the row stays unwritten, so the
+// give-up is recorded in the device status word like every other bounded wait (site 71).
+__device__ __forceinline__ bool wait_row(uint64_t* bar, DeviceStatus* status) {
   for (uint32_t spin = 0; spin < (1u << 24); ++spin)
     if (mbar_try_wait(bar, 0)) return true;
+  report_error(status, FLUXB_ERR_TIMEOUT, 71);
   return false;
 }
 
@@ -223,7 +225,8 @@ template <typename T, bool kLayerNorm>
 __global__ void __launch_bounds__(256, 4)
 norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, const T* __restrict__ shift,
                       T* __restrict__ y, float* __restrict__ rstd_out, int64_t rows, int cols,
-                      int64_t rows_per_batch, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps) {
+                      int64_t rows_per_batch, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps,
+                      DeviceStatus* status) {
   constexpr int VN = Vec<T>::N;
   extern __shared__ __align__(128) uint8_t bulk_smem[];
   const int warp = threadIdx.x >> 5;
@@ -241,7 +244,7 @@ norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, cons
     bulk_load_row(srow, x + xaddr.offset(row), row_bytes, &bars[warp]);
   }
   __syncwarp();
-  if (!wait_row(&bars[warp])) return;
+  if (!wait_row(&bars[warp], status)) return;
 
   const int nvec = cols / VN;
   float mean = 0.f;
@@ -301,14 +304,17 @@ static inline bool bulk_rows_ok(int64_t cols, size_t elt, const RowAddr& a) {
 }
 
 template <typename T, bool kLayerNorm>
-static void launch_norm_bulk(const T* x, const T* scale, const T* shift, T* y, float* rstd, int64_t rows,
-                             int64_t cols, int64_t rpb, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps,
-                             cudaStream_t st) {
+static int launch_norm_bulk(const T* x, const T* scale, const T* shift, T* y, float* rstd, int64_t rows,
+                            int64_t cols, int64_t rpb, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps,
+                            cudaStream_t st) {
   const size_t smem = 128 + 8 * (size_t)cols * sizeof(T);
   auto kern = norm_rows_bulk_kernel<T, kLayerNorm>;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess)
+    return set_error(FLUXB_ERR_CUDA, "row norm: cannot set shared memory size: %s", cudaGetErrorString(e));
   kern<<<(unsigned)((rows + 7) / 8), 256, smem, st>>>(x, scale, shift, y, rstd, rows, (int)cols, rpb, xaddr, y_ld,
-                                                       mod_stride, eps);
+                                                       mod_stride, eps, device_status_ptr());
+  return FLUXB_OK;
 }
 
 template <typename T>
@@ -324,8 +330,7 @@ static int launch_ln_mod(const void* x, const void* scale, const void* shift, vo
   {
     RowAddr xaddr{1, rows > 0 ? rows : 1, 0, 0, x_ld};
     if (bulk_rows_ok(cols, sizeof(T), xaddr) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-      launch_norm_bulk<T, true>(xp, sc, sh, yp, nullptr, rows, cols, rpb, xaddr, y_ld, mod_stride, eps, st);
-      return FLUXB_OK;
+      return launch_norm_bulk<T, true>(xp, sc, sh, yp, nullptr, rows, cols, rpb, xaddr, y_ld, mod_stride, eps, st);
     }
   }
 #define FLUXB_LN_CASE(G, VPL)                                                                  \
@@ -424,8 +429,7 @@ static int launch_rms(const void* x, const void* w, void* y, float* rstd, int64_
   T* yp = static_cast<T*>(y);
   const int64_t vecs = cols / VN;
   if (bulk_rows_ok(cols, sizeof(T), addr) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-    launch_norm_bulk<T, false>(xp, wp, nullptr, yp, rstd, rows, cols, 1, addr, cols, 0, eps, st);
-    return FLUXB_OK;
+    return launch_norm_bulk<T, false>(xp, wp, nullptr, yp, rstd, rows, cols, 1, addr, cols, 0, eps, st);
   }
 #define FLUXB_RMS_CASE(G, VPL)                                                                 \
   if (vecs == (G) * (VPL)) {                                                                   \
@@ -901,12 +905,12 @@ extern "C" int fluxb_layer_norm_modulation(const void* x, const void* scale, con
                      "layer_norm_modulation: cols/strides must be multiples of %d elements and "
                      "pointers 16-byte aligned", vn);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == FLUXB_BF16)
-    launch_ln_mod<__nv_bfloat16>(x, scale, shift, y, rows, cols, rows_per_batch, x_ld, y_ld,
-                                 mod_stride, eps, st);
-  else
-    launch_ln_mod<float>(x, scale, shift, y, rows, cols, rows_per_batch, x_ld, y_ld, mod_stride, eps,
-                         st);
+  const int rc = dtype == FLUXB_BF16
+                     ? launch_ln_mod<__nv_bfloat16>(x, scale, shift, y, rows, cols, rows_per_batch, x_ld, y_ld,
+                                                    mod_stride, eps, st)
+                     : launch_ln_mod<float>(x, scale, shift, y, rows, cols, rows_per_batch, x_ld, y_ld, mod_stride,
+                                            eps, st);
+  if (rc != FLUXB_OK) return rc;
   return launch_status("layer_norm_modulation");
 }
 
@@ -926,15 +930,14 @@ extern "C" int fluxb_rms_norm(const void* x, const void* w, void* y, float* rstd
                      "aligned", vn);
   RowAddr addr{n1, n2, s0, s1, s2};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == FLUXB_BF16)
-    launch_rms<__nv_bfloat16>(x, w, y, rstd, rows, cols, addr, eps, st);
-  else
-    launch_rms<float>(x, w, y, rstd, rows, cols, addr, eps, st);
+  const int rc = dtype == FLUXB_BF16 ? launch_rms<__nv_bfloat16>(x, w, y, rstd, rows, cols, addr, eps, st)
+                                     : launch_rms<float>(x, w, y, rstd, rows, cols, addr, eps, st);
+  if (rc != FLUXB_OK) return rc;
   return launch_status("rms_norm");
 }
 
-extern "C" int fluxb_rms_norm_bwd_partial_rows(int64_t rows) {
-  return (int)((rows + kRmsBwdRowsPerBlock - 1) / kRmsBwdRowsPerBlock);
+extern "C" int64_t fluxb_rms_norm_bwd_partial_rows(int64_t rows) {
+  return rows <= 0 ? 0 : (rows + kRmsBwdRowsPerBlock - 1) / kRmsBwdRowsPerBlock;
 }
 
 extern "C" int fluxb_rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd,

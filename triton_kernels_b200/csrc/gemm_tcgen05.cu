@@ -1,20 +1,21 @@
 // y = x · w^T with fused epilogues, as persistent, warp-specialised tcgen05 kernels.
 //
-// Two kernels share the role layout (192 threads):
-//   warp 0      TMA producer: streams 64-wide K slices of x and w (bf16, 128-byte swizzle)
-//               through a shared-memory ring.
-//   warp 1      MMA issuer: one thread issues tcgen05.mma from shared memory into one of two
-//               256-column fp32 accumulators in TMEM; tcgen05.commit releases ring slots and
-//               publishes finished accumulators.
-//   warps 2-5   epilogue: each warp reads its 32-lane TMEM quadrant with tcgen05.ld and applies
-//               bias / GELU / gate+residual in fp32.  Because there are two accumulators the
-//               epilogue of tile i overlaps the main loop of tile i+1.
+// Both kernels have one TMA producer warp (streams 64-wide K slices of x and w, bf16, 128-byte
+// swizzle, through a shared-memory ring), one MMA warp (the whole warp walks the loop, an elected
+// lane issues tcgen05.mma from shared memory into one of two 256-column fp32 accumulators in
+// TMEM; tcgen05.commit releases ring slots and publishes finished accumulators) and epilogue
+// warps that read their 32-lane TMEM quadrant with tcgen05.ld and apply bias / GELU /
+// gate+residual in fp32.  Two accumulators let the epilogue of tile i overlap the main loop of
+// tile i+1.
 //
-//   gemm_pair_kernel (default)  clusters of two CTAs share a 256x256 tile through
-//               cta_group::2 MMAs; 5-stage ring of 32 KB per CTA; output leaves through
-//               swizzled staging tiles and TMA stores; up to four problems per launch.
-//   gemm_kernel (FLUXB_GEMM_PAIR=0)  one CTA per 128x256 tile, 4-stage ring of 48 KB, direct
-//               16-byte stores.
+//   gemm_pair_kernel (default, 320 threads)  clusters of two CTAs share a 256x256 tile through
+//               cta_group::2 MMAs; 5-stage ring of 32 KB per CTA; EIGHT epilogue warps in two
+//               groups that take alternate 64-column pieces of a tile, each group with its own
+//               swizzled staging tile, named barrier and TMA-store-issuing thread; up to four
+//               problems per launch.  Second instantiation: the q|k|v head epilogue (QK RMS norm,
+//               RoPE, head-major layout through a 5-D TMA store).
+//   gemm_kernel (FLUXB_GEMM_PAIR=0, 192 threads)  one CTA per 128x256 tile, 4-stage ring of
+//               48 KB, four epilogue warps, direct 16-byte stores.
 //
 // Tiles are handed out statically (tile = id + i * stride) in an L2-aware order (tile_coords).
 // Edge tiles rely on TMA zero fill for loads and on TMA clipping / masks for stores.  Every
@@ -750,11 +751,6 @@ static int prepare_problem(const fluxb_linear_problem& a, int64_t N, int64_t K, 
       p.raster_band_n = 1;  // keep w row-blocks
       p.raster_group = w_bytes <= keep_limit ? tn : (concurrent / tm > 1 ? concurrent / tm : 1);
     }
-    static const char* renv = getenv("FLUXB_GEMM_RASTER");  // "band_n,group" override for experiments
-    if (renv != nullptr && *renv != 0) {
-      int bn = 0, gr = 0;
-      if (sscanf(renv, "%d,%d", &bn, &gr) == 2 && gr > 0) { p.raster_band_n = bn; p.raster_group = gr; }
-    }
     if (p.raster_group < 1) p.raster_group = 1;
   }
   return FLUXB_OK;
@@ -832,6 +828,10 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: 1..%d problems with their stream descriptions", fluxb::gemm2::MAX_PROBLEMS);
   if (!use_pair_kernel()) return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: needs the CTA-pair kernel (FLUXB_GEMM_PAIR=0 is set)");
   if (D != 128) return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: head_dim %lld (only 128)", (long long)D);
+  // A 256-column tile holds two heads and is normalised as a whole with q's, k's or no scale: the
+  // q|k and k|v boundaries (multiples of H*D) must therefore fall on tile boundaries.
+  if ((H * D) % 256)
+    return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: %lld heads (the head count must be even)", (long long)H);
   if (B <= 0 || H <= 0 || L_total <= 0 || K <= 0 || B > 65535 || H > 65535 || L_total > (1 << 30))
     return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: bad sizes");
   if (!qkv_out || !aligned16(qkv_out)) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: output null or misaligned");

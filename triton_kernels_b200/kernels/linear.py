@@ -12,10 +12,6 @@ class UnsupportedDtype(KeyError, TypeError):
     TypeError so callers can catch either."""
 
 
-# Benchmarks set this to a list to collect (M, N, K, start_event, end_event) per GEMM launch.
-launch_probe: list | None = None
-
-
 def linear_into(
     x2d: torch.Tensor,
     w: torch.Tensor,
@@ -39,9 +35,6 @@ def linear_into(
     assert x2d.stride(1) == 1 and w.stride(1) == 1 and y.stride(1) == 1
     if split is None:
         split = N
-    if launch_probe is not None:
-        ev0 = torch.cuda.Event(enable_timing=True)
-        ev0.record()
     _lib.check(
         _lib.load().fluxb_linear(
             _lib.ptr(x2d), _lib.ptr(w), _lib.ptr(b), _lib.ptr(y), M, N, K,
@@ -52,10 +45,6 @@ def linear_into(
             _lib.stream_handle(),
         )
     )
-    if launch_probe is not None:
-        ev1 = torch.cuda.Event(enable_timing=True)
-        ev1.record()
-        launch_probe.append((M, N, K, ev0, ev1))
 
 
 def linear_grouped_into(
@@ -89,25 +78,20 @@ def linear_grouped_into(
             slot.resid, slot.ldr = _lib.ptr(resid), (resid.stride(0) if resid is not None else 0)
             slot.gate, slot.gate_stride = _lib.ptr(gate), pr.get("gate_stride", 0)
             slot.rows_per_batch = pr.get("rows_per_batch", 1)
-        if launch_probe is not None:
-            ev0 = torch.cuda.Event(enable_timing=True)
-            ev0.record()
         _lib.check(
             _lib.load().fluxb_linear_grouped(arr, len(chunk), N, K, epi, split, epi2, int(round_before_act), _lib.stream_handle())
         )
-        if launch_probe is not None:
-            ev1 = torch.cuda.Event(enable_timing=True)
-            ev1.record()
-            launch_probe.append((tuple(pr["x2d"].shape[0] for pr in chunk), N, K, ev0, ev1))
 
 
-def qkv_projection_supported(stream_lengths, head_dim: int) -> bool:
-    """Whether linear_qkv_grouped_into takes these streams (see its docstring)."""
+def qkv_projection_supported(stream_lengths, head_dim: int, num_heads: int) -> bool:
+    """Whether linear_qkv_grouped_into takes these streams (see its docstring).  The head count
+    must be even: an output tile is 256 columns = two heads and is treated as a whole as q, k or v."""
     import os
 
     if os.environ.get("FLUXB_GEMM_PAIR", "1") == "0":  # the single-CTA kernel has no such epilogue
         return False
-    return head_dim == 128 and 1 <= len(stream_lengths) <= 4 and all(L > 0 and L % 128 == 0 for L in stream_lengths)
+    return (head_dim == 128 and num_heads % 2 == 0 and 1 <= len(stream_lengths) <= 4
+            and all(L > 0 and L % 128 == 0 for L in stream_lengths))
 
 
 def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_out: torch.Tensor, eps: float = 1e-6,
@@ -149,17 +133,10 @@ def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_ou
         slot.rows_per_batch = x.shape[1]
         d.pe, d.q_scale, d.k_scale, d.row_offset = _lib.ptr(pe_c), _lib.ptr(qs), _lib.ptr(ks), row
         row += x.shape[1]
-    if launch_probe is not None:
-        ev0 = torch.cuda.Event(enable_timing=True)
-        ev0.record()
     _lib.check(
         _lib.load().fluxb_linear_qkv_grouped(arr, desc, len(streams), B, H, D, L, K, _lib.ptr(qkv_out), eps, N2, epi2,
                                              int(round_before_act), _lib.stream_handle())
     )
-    if launch_probe is not None:
-        ev1 = torch.cuda.Event(enable_timing=True)
-        ev1.record()
-        launch_probe.append((tuple(B * st["x"].shape[1] for st in streams), 3 * H * D + N2, K, ev0, ev1))
 
 
 def _as_2d(x: torch.Tensor, K: int) -> torch.Tensor:

@@ -66,10 +66,12 @@ class _rms_norm(torch.autograd.Function):
             x = x.contiguous()
         dims = [1] * (3 - len(lead)) + list(lead)
         strides = [0] * (3 - len(lead)) + list(x.stride()[:-1])
+        # decided on the caller's tensors: the cast copy of `scale` below never requires grad
+        need_grad = any(ctx.needs_input_grad[:2])
+        ctx.scale_dtype = scale.dtype
         scale = scale.to(x.dtype).contiguous()
         y = torch.empty(x.shape, device=x.device, dtype=x.dtype)
         M = y.numel() // N
-        need_grad = x.requires_grad or scale.requires_grad
         rstd = torch.empty((M,), dtype=torch.float32, device=x.device) if need_grad else None
         _lib.check(
             _lib.load().fluxb_rms_norm(
@@ -98,7 +100,7 @@ class _rms_norm(torch.autograd.Function):
                 M, N, _lib.dtype_code(xc), _lib.stream_handle(),
             )
         )
-        dw = dw_partial.sum(dim=0).to(w.dtype)
+        dw = dw_partial.sum(dim=0).to(ctx.scale_dtype)
         return dx.reshape(x.shape), dw, None
 
 

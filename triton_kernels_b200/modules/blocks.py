@@ -14,8 +14,8 @@ triton_kernels/modules/blocks.py:78-172 (and therefore of triton_kernels/flux/la
   linear1 -> split ; GELU ; cat ; linear2        GEMM with a column-split epilogue that writes
                                                    GELU(mlp) next to where attention writes
 
-About 9 launches per double-stream stream pair instead of about 40, and no elementwise pass
-over [L, C] outside a GEMM epilogue.  LayerNorm uses eps 1e-6 like the PyTorch blocks of
+11 launches per double-stream block (5 per single-stream block) instead of about 40, and no
+elementwise pass over [L, C] outside a GEMM epilogue.  LayerNorm uses eps 1e-6 like the PyTorch blocks of
 triton_kernels/flux/layers.py:162,165,247 (the reference kernel blocks pass 1e-5; the
 difference is far below bf16 resolution).
 """
@@ -241,7 +241,7 @@ class SingleStreamBlock(nn.Module):
         # linear1: columns [0, 3C) -> qkv, columns [3C, 3C+M) -> GELU -> cat[:, :, C:]
         cat = torch.empty((B, L, C + M), device=x.device, dtype=x.dtype)  # attn | gelu(mlp)
         sp = self.sequence_parallel
-        if ((sp is None or sp.world == 1) and self.fuse_qkv_epilogue and qkv_projection_supported((L,), D)
+        if ((sp is None or sp.world == 1) and self.fuse_qkv_epilogue and qkv_projection_supported((L,), D, H)
                 and (3 * C) % 256 == 0 and M % 8 == 0):
             # one GEMM: the q|k|v columns leave normalised, rotated and head-major, the MLP columns
             # through GELU into the concat buffer
@@ -333,7 +333,7 @@ class DoubleStreamBlock(nn.Module):
 
         h1 = [h_txt, h_img]
         sp = self.sequence_parallel
-        if (sp is None or sp.world == 1) and self.fuse_qkv_epilogue and qkv_projection_supported(Ls, D):
+        if (sp is None or sp.world == 1) and self.fuse_qkv_epilogue and qkv_projection_supported(Ls, D, H):
             # both streams' qkv projections in one launch whose epilogue also does the QK norm, the
             # rotation and the head-major text|image layout attention reads
             qkv_heads = torch.empty((3, B, H, Lt + Li, D), device=dev, dtype=dt)

@@ -61,6 +61,21 @@ class SequenceParallel:
             pb.arena.close()
         self._peer = {}
 
+    def check(self) -> None:
+        """Call at a step boundary (it synchronises the device): raises FluxbError if a kernel of
+        this rank gave up a bounded wait since the last check.  The flag waits of the peer exchange
+        (status sites 61 and 62) stop after two seconds and the stream then carries on with
+        whatever the arena holds, so a rank whose peer was held up that long (first-call module
+        load, a paused process) has computed attention on stale data; the device status word is
+        the only trace.  The word is cleared by the read."""
+        from .. import _lib
+
+        code, where = _lib.device_status()
+        if code != 0:
+            what = "a peer-exchange flag wait" if where in (61, 62) else "a kernel"
+            raise _lib.FluxbError(f"{what} on rank {self.rank} reported error {code} at site {where}: "
+                                  "the outputs of the steps since the last check are not valid")
+
     # ---- token-sharded -> head-sharded -------------------------------------------------
     def send_layout(self, B: int, L_loc: int, H: int, D: int) -> tuple[tuple[int, ...], tuple[int, int, int, int, int]]:
         """Shape of the send buffer and the (heads_per_group, batch, group, head, row) strides
