@@ -330,13 +330,19 @@ def run_micro(which: str, steps: int, warmup: int, impl: str = "b200"):
             graph.replay()
         torch.cuda.synchronize()
         reps = max(steps, 1)
+        sampler = ClockSampler(0, period_s=0.002)
+        sampler.start()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(reps):
             graph.replay()
         b.record()
         torch.cuda.synchronize()
+        last_clocks.clear()
+        last_clocks.update(sampler.stop())
         return a.elapsed_time(b) * 1e-3 / (reps * len(calls))
+
+    last_clocks: dict = {}  # clock record of the most recent time_calls()
 
     def sets_for(bytes_per_set):
         return max(2, int(300e6 // bytes_per_set) + 1)
@@ -347,7 +353,9 @@ def run_micro(which: str, steps: int, warmup: int, impl: str = "b200"):
         else:
             ach, peak, unit = work / sec / 1e12, peaks["bf16_tflops"], "TFLOP/s"
         print(json.dumps({"micro": name, "impl": impl, "us_per_launch": sec * 1e6, "bound": bound, "achieved": ach,
-                          "peak": peak, "unit": unit, "frac": ach / peak, "algorithmic_work": work}), flush=True)
+                          "peak": peak, "unit": unit, "frac": ach / peak, "algorithmic_work": work,
+                          "sm_mhz": last_clocks.get("sm_mhz"), "sm_mhz_min": last_clocks.get("sm_mhz_min"),
+                          "power_w_max": last_clocks.get("power_w_max"), "reasons": last_clocks.get("reasons")}), flush=True)
 
     def want(name):
         return which in ("all", name)
@@ -490,9 +498,14 @@ def _reference_dit(ref, depth: int, depth_single: int):
             self.final_layer = RL.LastLayer(C, 1, 64)
 
         def forward(self, img, txt, t, gd, pe):
+            # the reference's timestep_embedding builds its frequencies on the host on every call
+            # (triton_kernels/flux/layers.py:66), which a CUDA-graph capture cannot contain; this
+            # package's device-side form of the same formula stands in for it
+            from triton_kernels_b200.flux.model import timestep_embedding
+
             img = self.img_in(img)
-            vec = self.time_in(RL.timestep_embedding(t, 256).to(img.dtype))
-            vec = vec + self.guidance_in(RL.timestep_embedding(gd, 256).to(img.dtype))
+            vec = self.time_in(timestep_embedding(t, 256).to(img.dtype))
+            vec = vec + self.guidance_in(timestep_embedding(gd, 256).to(img.dtype))
             txt = self.txt_in(txt)
             for blk in self.double_blocks:
                 img, txt = blk(img=img, txt=txt, vec=vec, pe=pe)

@@ -1,12 +1,15 @@
-// Non-causal flash attention forward for head_dim 128, bf16, on tcgen05 + TMEM.
+// Non-causal flash attention forward for head_dim 128 or 64, bf16, on tcgen05 + TMEM.
 //
 // One CTA owns 256 query rows of one (batch, head) as two 128-row tiles and walks the keys in
-// tiles of 128.  Roles (320 threads):
+// tiles of 128.  Roles (384 threads = three warpgroups):
 //   warps 0-3   softmax group 0: thread r owns query row r of tile 0
 //   warps 4-7   softmax group 1: same for tile 1
 //   warp  8     TMA producer: Q once, then K_j, V_j through a 4-slot ring of 32 KB tiles
 //   warp  9     MMA issuer (whole warp walks the loop, one elected lane issues): S_t = Q_t K_j^T and
 //               O_t += P_t V_j
+//   warps 10-11 idle: they complete the third warpgroup, which hands most of its registers to the
+//               softmax warpgroups (setmaxnreg: 56 against 224 per thread), so that a thread's 128
+//               scores stay in registers without spills
 // TMEM (512 columns): S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  P_t (bf16) is written back
 // over the first 64 columns of S_t by the softmax threads and fed to the second MMA straight
 // from TMEM, so probabilities never touch shared memory.  While group 0 does softmax on S_0 the
@@ -26,7 +29,7 @@ constexpr int BKV = 128;            // keys per tile
 constexpr int HALF_BYTES = 128 * 128;  // [128 rows][64 bf16] swizzled block
 __host__ __device__ constexpr int tile_bytes(int d) { return (d / 64) * HALF_BYTES; }  // one Q, K or V tile: 128 rows x d
 constexpr int KV_SLOTS = 4;
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;
 constexpr int TMEM_COLS = 512;
 __host__ __device__ constexpr int smem_bytes(int d) { return 2 * tile_bytes(d) + KV_SLOTS * tile_bytes(d) + 1024 + 256; }
 constexpr float kRescaleThreshold = 8.0f;
@@ -165,6 +168,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Registers move from the third warpgroup to the softmax warpgroups.  Each setmaxnreg sits
+  // inside the branch whose code it governs, and what the one side releases (128 x 112) is
+  // exactly what the other side takes (256 x 56): an increase waits for registers released
+  // inside this CTA.
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -276,8 +285,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       }
     }
     __syncwarp();
+  }
   } else {
     // ------------------------------------------------------------------ softmax groups
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int t = warp >> 2;   // query tile / group
     const int quad = warp & 3;  // TMEM lane quadrant
     const int row = q0 + t * BQ + quad * 32 + lane;
@@ -413,12 +424,6 @@ static int encode_qkv_map(CUtensorMap* tm, const void* base, int64_t B, int64_t 
   return encode_tmap_bf16(tm, base, 4, dims, strides, box);
 }
 
-static uint32_t env_u32(const char* name, uint32_t dflt) {
-  const char* s = getenv(name);
-  if (s == nullptr || *s == 0) return dflt;
-  return (uint32_t)strtoul(s, nullptr, 0);
-}
-
 static int attention_impl(const void* q, const void* k, const void* v, void* o, int64_t B,
                           int64_t H, int64_t Lq, int64_t Lk, int64_t D, int64_t q_sb,
                           int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
@@ -470,14 +475,8 @@ static int attention_impl(const void* q, const void* k, const void* v, void* o, 
   p.rows_per_rank = n_ranks > 0 ? (int)rows_per_rank : 0;
   for (int i = 0; i < 8; ++i) p.o_rank[i] = i < n_ranks ? static_cast<__nv_bfloat16*>(o_bases[i]) : nullptr;
 
-  // Every fourth pair of a row takes the polynomial exp2 unless FLUXB_ATTN_POLY=0 (all on MUFU).
-  static const int poly_env = (int)env_u32("FLUXB_ATTN_POLY", 4);
-  auto kern = attn_kernel<4, 128>;
-  if (D == 128) {
-    if (poly_env == 0) kern = attn_kernel<1000, 128>;
-  } else {
-    kern = poly_env == 0 ? attn_kernel<1000, 64> : attn_kernel<4, 64>;
-  }
+  // Every fourth pair of a row takes the polynomial exp2.
+  auto kern = D == 128 ? attn_kernel<4, 128> : attn_kernel<4, 64>;
   const int smem = smem_bytes((int)D);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: cannot set shared memory size: %s", cudaGetErrorString(e));

@@ -69,6 +69,8 @@ __device__ __forceinline__ void forget(uint4& t) {
   asm volatile("" : "+r"(t.x), "+r"(t.y), "+r"(t.z), "+r"(t.w));
 }
 
+__device__ __forceinline__ uint4 ld_nc_u4(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
 template <int G>
 __device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
@@ -79,7 +81,16 @@ __device__ __forceinline__ float group_sum(float v) {
 // Row addressing through a 3-level stride (head-split views): row -> element offset.
 struct RowAddr {
   int64_t n1, n2, s0, s1, s2;
+  // Set by the host when all rows follow each other at stride s2 (a contiguous tensor): no index
+  // split then; the 64-bit divisions of the general case cost more than a 128-wide row's math.
+  int flat;
   __device__ __forceinline__ int64_t offset(int64_t row) const {
+    if (flat) return row * s2;
+    if (row < (1ll << 31) && n1 < (1ll << 31) && n2 < (1ll << 31)) {
+      const uint32_t r = (uint32_t)row, d2 = (uint32_t)n2, d1 = (uint32_t)n1;
+      const uint32_t t = r / d2, i2 = r - t * d2, i0 = t / d1, i1 = t - i0 * d1;
+      return (int64_t)i0 * s0 + (int64_t)i1 * s1 + (int64_t)i2 * s2;
+    }
     const int64_t i2 = row % n2;
     const int64_t t = row / n2;
     return (t / n1) * s0 + (t % n1) * s1 + i2 * s2;
@@ -328,7 +339,7 @@ static int launch_ln_mod(const void* x, const void* scale, const void* shift, vo
   T* yp = static_cast<T*>(y);
   const int64_t vecs = cols / VN;
   {
-    RowAddr xaddr{1, rows > 0 ? rows : 1, 0, 0, x_ld};
+    RowAddr xaddr{1, rows > 0 ? rows : 1, 0, 0, x_ld, 1};
     if (bulk_rows_ok(cols, sizeof(T), xaddr) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
       return launch_norm_bulk<T, true>(xp, sc, sh, yp, nullptr, rows, cols, rpb, xaddr, y_ld, mod_stride, eps, st);
     }
@@ -391,6 +402,44 @@ rms_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
   }
 }
 
+// Narrow rows (one 16-byte vector per lane, e.g. the 128-wide per-head rows of q and k): a
+// group of G lanes walks R rows with all R loads issued before the first reduction, so that a
+// thread has R x 16 bytes in flight instead of 16 (at 1024 threads per SM that is 64 KB per SM,
+// enough to cover HBM latency at full bandwidth).
+template <typename T, int G, int R>
+__global__ void __launch_bounds__(256, 4)
+rms_narrow_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                       float* __restrict__ rstd_out, int64_t rows, int cols, RowAddr addr, float eps) {
+  constexpr int VN = Vec<T>::N;
+  const int lig = threadIdx.x % G;
+  const int64_t gpb = blockDim.x / G;
+  const int64_t row0 = (blockIdx.x * gpb + threadIdx.x / G) * R;
+  uint4 raw[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int64_t r = row0 + i < rows ? row0 + i : rows - 1;
+    raw[i] = ld_nc_u4(x + addr.offset(r) + lig * VN);
+  }
+  Vec<T> wv;
+  wv.load_nc(w + lig * VN);
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    Vec<T> t;
+    t.unpack(raw[i]);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < VN; ++j) s += t.v[j] * t.v[j];
+    const float rstd = rsqrtf(group_sum<G>(s) / cols + eps);
+    const int64_t r = row0 + i;
+    if (r < rows) {
+      if (rstd_out != nullptr && lig == 0) rstd_out[r] = rstd;
+#pragma unroll
+      for (int j = 0; j < VN; ++j) t.v[j] = t.v[j] * rstd * wv.v[j];
+      t.store(y + r * (int64_t)cols + lig * VN);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 rms_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
@@ -438,7 +487,16 @@ static int launch_rms(const void* x, const void* w, void* y, float* rstd, int64_
         xp, wp, yp, rstd, rows, (int)cols, addr, eps);                                         \
     return FLUXB_OK;                                                                           \
   }
-  FLUXB_RMS_CASE(8, 1) FLUXB_RMS_CASE(16, 1) FLUXB_RMS_CASE(32, 1) FLUXB_RMS_CASE(32, 2)
+#define FLUXB_RMS_NARROW(G)                                                                    \
+  if (vecs == (G)) {                                                                           \
+    const int64_t rpb = (256 / (G)) * 4;                                                       \
+    rms_narrow_rows_kernel<T, G, 4><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, st>>>(       \
+        xp, wp, yp, rstd, rows, (int)cols, addr, eps);                                         \
+    return FLUXB_OK;                                                                           \
+  }
+  FLUXB_RMS_NARROW(8) FLUXB_RMS_NARROW(16) FLUXB_RMS_NARROW(32)
+#undef FLUXB_RMS_NARROW
+  FLUXB_RMS_CASE(32, 2)
   FLUXB_RMS_CASE(32, 3) FLUXB_RMS_CASE(32, 4) FLUXB_RMS_CASE(32, 6) FLUXB_RMS_CASE(32, 8)
   FLUXB_RMS_CASE(32, 12) FLUXB_RMS_CASE(32, 16) FLUXB_RMS_CASE(32, 24)
 #undef FLUXB_RMS_CASE
@@ -928,7 +986,8 @@ extern "C" int fluxb_rms_norm(const void* x, const void* w, void* y, float* rstd
     return set_error(FLUXB_ERR_BAD_ARG,
                      "rms_norm: cols/strides must be multiples of %d elements and pointers 16-byte "
                      "aligned", vn);
-  RowAddr addr{n1, n2, s0, s1, s2};
+  const int flat = (n1 == 1 || s1 == n2 * s2) && (n0 == 1 || s0 == n1 * n2 * s2);
+  RowAddr addr{n1, n2, s0, s1, s2, flat};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rc = dtype == FLUXB_BF16 ? launch_rms<__nv_bfloat16>(x, w, y, rstd, rows, cols, addr, eps, st)
                                      : launch_rms<float>(x, w, y, rstd, rows, cols, addr, eps, st);
