@@ -281,6 +281,9 @@ norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, cons
   }
   const float rstd = rsqrtf(warp_sum(q) / cols + eps);
   if (!kLayerNorm && rstd_out != nullptr && lane == 0) rstd_out[row] = rstd;
+  // The result replaces the row in shared memory and leaves as ONE bulk copy, like it came: the
+  // lanes issue no global stores and the warp's last act is to wait until the copy engine has
+  // read the staged row.
   T* yr = y + row * y_ld;
   if (kLayerNorm) {
     const int64_t b = row / rows_per_batch;
@@ -293,7 +296,7 @@ norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, cons
       d.load_nc(sh + i * VN);
 #pragma unroll
       for (int j = 0; j < VN; ++j) t.v[j] = (t.v[j] - mean) * rstd * (1.0f + a.v[j]) + d.v[j];
-      t.store(yr + i * VN);
+      t.store(srow + i * VN);
     }
   } else {
     for (int i = lane; i < nvec; i += 32) {
@@ -302,9 +305,19 @@ norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, cons
       wv.load_nc(scale + i * VN);
 #pragma unroll
       for (int j = 0; j < VN; ++j) t.v[j] = t.v[j] * rstd * wv.v[j];
-      t.store(yr + i * VN);
+      t.store(srow + i * VN);
     }
   }
+  fence_proxy_async_smem();  // each lane's writes, before the async proxy reads them
+  __syncwarp();
+  if (lane == 0) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(reinterpret_cast<uint64_t>(yr)),
+                 "r"(smem_u32(srow)), "r"(row_bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  }
+  __syncwarp();
 }
 
 // True when the bulk-copy kernel applies: rows of 2-24 KB, 16-byte multiples, 16-byte aligned.
