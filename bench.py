@@ -430,6 +430,21 @@ def run_micro(which: str, steps: int, warmup: int, impl: str = "b200"):
         else:
             calls = [lambda x=x, w=w, b=b: ref.linear(x, w, b, activation="GELU") for x, w, b, _ in bufs]
         emit("linear_bias_gelu[M4608,K3072,N12288]", time_calls(calls), 2.0 * M * N * K, "tensor")
+    if want("linear_down") and ours:
+        # the other GEMMs of a block step as it launches them: both streams grouped, gate/residual epilogue
+        from triton_kernels_b200.kernels.linear import linear_grouped_into
+        Lt_, Li_ = 512, L - 512
+        for name, K_ in (("linear_proj_gate_resid[M512+4096,K3072,N3072]", Cc), ("linear_mlp_down_gate_resid[M512+4096,K12288,N3072]", 4 * Cc)):
+            bufs = []
+            for _ in range(2):
+                probs = []
+                for M_ in (Lt_, Li_):
+                    probs.append(dict(x2d=randn(M_, K_), w=randn(Cc, K_, std=0.02), b=randn(Cc, std=0.02),
+                                      y=torch.empty(M_, Cc, device=dev, dtype=BF), resid=randn(M_, Cc), gate=randn(1, Cc),
+                                      gate_stride=0, rows_per_batch=M_))
+                bufs.append(probs)
+            calls = [lambda pr=pr: linear_grouped_into(pr, epi=_lib.EPI_GATE_RESID) for pr in bufs]
+            emit(name, time_calls(calls), 2.0 * L * Cc * K_, "tensor")
     if want("linear_qkv") and ours:
         # both streams' q|k|v projection with QK norm, RoPE and the head-major layout in the epilogue
         from triton_kernels_b200.kernels.linear import linear_qkv_grouped_into
@@ -963,7 +978,7 @@ def main():
                     "all | linear | attention | layer_norm | rms_norm | rope (--steps = timed calls per point)")
     ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")
     ap.add_argument("--micro", default=None, help="per-kernel microbenchmark: all | linear_qkv | layer_norm_modulation | rms_norm | "
-                    "rope | qkv_prepare | modulation_projection | linear_gelu | attention")
+                    "rope | qkv_prepare | modulation_projection | linear_gelu | linear_down | attention")
     args = ap.parse_args()
     gpu_impl = "triton_ref" if args.impl == "triton_ref" else "b200"
     if args.micro:
