@@ -638,7 +638,7 @@ def run_dit(steps: int, warmup: int, impl: str = "b200"):
 # ranks and an all-to-all on heads around attention.  Strong scaling: the total work is fixed.
 # --------------------------------------------------------------------------------------
 def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: int, exchange: str,
-                    single_rank_baseline: bool = False) -> dict:
+                    single_rank_baseline: bool = False, scatter_from_projection: bool = False) -> dict:
     """One double-stream block over 16384 image + 512 text tokens with the tokens sharded over the
     ranks of the default process group (which the caller has initialised when world > 1).  With
     `single_rank_baseline` every rank first times the unsharded block on its own GPU, so that the
@@ -692,7 +692,7 @@ def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: 
         if single_rank_baseline or world == 1:
             single_ms = timed(lambda: block(img, txt, vec, pe))
         if world > 1:
-            sp = block.sequence_parallel = SequenceParallel(exchange=exchange)
+            sp = block.sequence_parallel = SequenceParallel(exchange=exchange, scatter_from_projection=scatter_from_projection)
             txt_l, img_l, pe_l = shard_joint_sequence(txt, img, pe, rank, world)
             del img, txt
             sampler = ClockSampler(local_rank)
@@ -710,8 +710,9 @@ def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: 
         "workload": f"flux_double_stream_block hidden {C}, {H} heads x 128, {li} image + {lt} text tokens, batch 1 in total, "
                     "weights N(0,0.02), seed 4",
         "parallelism": f"ulysses sequence-parallel x{world}", "scaling": "strong",
-        "exchange": ("stores into peer memory from the producing kernels" if exchange == "peer" else "NCCL all-to-all")
-                    if world > 1 else None,
+        "exchange": (("stores into peer memory from the producing kernels"
+                      + (" (q|k|v from the projection's epilogue)" if scatter_from_projection else ""))
+                     if exchange == "peer" else "NCCL all-to-all") if world > 1 else None,
         "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "steps": steps, "warmup": warmup,
         "block_tflop": flop / 1e12, "tflops_per_gpu": flop / (ms * 1e-3) / 1e12 / world,
     }
@@ -765,7 +766,8 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    rec = ulysses_measure(rank, local_rank, world, args.steps, args.warmup, args.exchange, single_rank_baseline=True)
+    rec = ulysses_measure(rank, local_rank, world, args.steps, args.warmup, args.exchange, single_rank_baseline=True,
+                          scatter_from_projection=args.sp_scatter_from_projection)
     if rank == 0:
         print(json.dumps({
             "metric": "flux_double_block_fwd_tokens_per_s", "value": rec["tokens_per_s"], "unit": UNIT,
@@ -974,6 +976,9 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="--parallel ulysses: how heads and tokens are exchanged around attention: stores into peer "
                          "memory from the producing kernels (default) or two NCCL all-to-alls")
+    ap.add_argument("--sp-scatter-from-projection", action="store_true",
+                    help="--parallel ulysses with the peer exchange: the q|k|v projection's epilogue stores into the peers' "
+                         "arenas itself instead of the assembly kernel after it (measured slower on two GPUs)")
     ap.add_argument("--sweep", default=None, help="sequence-length sweep with the reference benchmark scripts' shapes: "
                     "all | linear | attention | layer_norm | rms_norm | rope (--steps = timed calls per point)")
     ap.add_argument("--dit", action="store_true", help="time the full 19+38 block DiT step instead of one block")
@@ -1015,7 +1020,11 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a short collective timeout: a rank that fails inside a sub-record ends the others' next
+        # collective with an error (recorded in the line) instead of stalling the run
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     import triton_kernels_b200 as tk
     from triton_kernels_b200 import _lib
@@ -1202,19 +1211,59 @@ def main():
         raise SystemExit(f"device status word reports error {code} at {where}")
 
     # ---------------------------------------------------------------- sub-records (all ranks take part)
+    # A sub-record that fails must not take the headline line with it: its error is recorded in its
+    # place, and the sub-records after it are skipped (after a failed collective the ranks may no
+    # longer be in step).
     extras = {}
+    extras_ok = True
+
+    def guarded(name, fn):
+        nonlocal extras_ok
+        if not extras_ok:
+            extras[name] = {"skipped": "an earlier sub-record failed"}
+            return
+        try:
+            extras[name] = fn()
+        except BaseException as e:  # noqa: BLE001
+            if isinstance(e, KeyboardInterrupt):
+                raise
+            extras[name] = {"error": repr(e)[:400]}
+            extras_ok = False
+
     if not args.no_extras:
-        extras["host_copy"] = host_copy_probe(dev, barrier, max_over_ranks)
+        guarded("host_copy", lambda: host_copy_probe(dev, barrier, max_over_ranks))
         del block, graphed
         torch.cuda.empty_cache()
-        dit = dit_measure(dev, min(args.steps, 20), min(args.warmup, 3), barrier=barrier, max_over_ranks=max_over_ranks)
-        dit["tokens_per_s"] = world * dit["tokens_per_s_per_gpu"]
-        dit["e2e"]["tokens_per_s"] = world * dit["e2e"]["tokens_per_s_per_gpu"]
-        dit["parallelism"] = f"batch data-parallel x{world}: one full DiT step per GPU per step" if world > 1 else "single GPU"
-        extras["dit"] = dit
+
+        def dit_record():
+            dit = dit_measure(dev, min(args.steps, 20), min(args.warmup, 3), barrier=barrier, max_over_ranks=max_over_ranks)
+            dit["tokens_per_s"] = world * dit["tokens_per_s_per_gpu"]
+            dit["e2e"]["tokens_per_s"] = world * dit["e2e"]["tokens_per_s_per_gpu"]
+            dit["parallelism"] = (f"batch data-parallel x{world}: one full DiT step per GPU per step" if world > 1
+                                  else "single GPU")
+            return dit
+
+        guarded("dit", dit_record)
         if world > 1 and H % world == 0:
-            extras["ulysses"] = ulysses_measure(rank, local_rank, world, min(args.steps, 20), args.warmup, args.exchange,
-                                                single_rank_baseline=True)
+            # both exchanges; the record's own figures are those of the faster one, the other's
+            # step time sits beside them
+            def ulysses_record():
+                recs = {ex: ulysses_measure(rank, local_rank, world, min(args.steps, 20), args.warmup, ex,
+                                            single_rank_baseline=(ex == "peer")) for ex in ("peer", "nccl")}
+                single = recs["peer"]["single_gpu_ms_per_step"]
+                for r in recs.values():
+                    r["single_gpu_ms_per_step"] = single
+                    r["efficiency_vs_single_gpu"] = single / (world * r["ms_per_step"])
+                best = min(recs, key=lambda ex: recs[ex]["ms_per_step"])
+                out = dict(recs[best])
+                out["ms_per_step_by_exchange"] = {ex: r["ms_per_step"] for ex, r in recs.items()}
+                out["efficiency_by_exchange"] = {ex: r["efficiency_vs_single_gpu"] for ex, r in recs.items()}
+                for k in ("assembly_scatter_kernel_ms", "assembly_scatter_nvlink_gbs_per_gpu"):
+                    if k in recs["peer"]:
+                        out[k] = recs["peer"][k]
+                return out
+
+            guarded("ulysses", ulysses_record)
 
     # Peak for the roofline fraction: the cuBLAS figure of the clock regime the timed launches ran
     # in.  Near the maximum SM clock they are a burst (the power cap has not bitten yet) and the
@@ -1283,8 +1332,12 @@ def main():
         if "parity" in line and max(line["parity"]["rel_l2_img"], line["parity"]["rel_l2_txt"]) > 1e-2:
             raise SystemExit("the timed step's outputs differ from the CPU oracle by more than 1e-2 relative L2")
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        try:
+            if extras_ok:
+                dist.barrier()
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001  (a rank that failed a sub-record may already be gone)
+            pass
 
 
 if __name__ == "__main__":

@@ -255,6 +255,21 @@ int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_q
                              int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K, void* qkv_out,
                              float eps, int64_t N2, int epi2, int round_before_act, fluxb_stream_t stream);
 
+/*
+ * fluxb_linear_qkv_grouped with one output base per head group instead of qkv_out (the
+ * sequence-parallel form; no counterpart in the reference, whose blocks know one GPU): heads
+ * [g*H/n_groups, (g+1)*H/n_groups) of q land at group_bases[g] + b*o_sb + (h % (H/n_groups))*o_sh
+ * + l*o_sl with l = row_offset + row, those of k and v k_off and v_off elements further, written
+ * with plain 16-byte stores (the bases may point into other ranks' arenas, as for
+ * fluxb_qkv_prep_scatter).  Rows are masked one by one: with B == 1 the stream lengths and row
+ * offsets need not be multiples of 128.
+ */
+int fluxb_linear_qkv_grouped_scatter(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
+                                     int count, int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K,
+                                     void* const* group_bases, int n_groups, int64_t k_off, int64_t v_off,
+                                     int64_t o_sb, int64_t o_sh, int64_t o_sl, float eps, int64_t N2, int epi2,
+                                     int round_before_act, fluxb_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * Sequence-parallel (Ulysses) exchange over peer memory.  The reference has no multi-GPU path,
  * so nothing in this section replaces a reference function; the entry points exist so that the
@@ -311,6 +326,23 @@ int fluxb_attention_scatter(const void* q, const void* k, const void* v, void* c
                             int64_t k_sb, int64_t k_sh, int64_t k_sl, int64_t v_sb, int64_t v_sh,
                             int64_t v_sl, int64_t o_sb, int64_t o_sh, int64_t o_sl, float sm_scale,
                             fluxb_stream_t stream);
+
+/*
+ * fluxb_attention / fluxb_attention_scatter with the keys cut into k_splits ranges that run as
+ * separate CTAs, plus a merge pass (no counterpart in the reference; its kernel
+ * triton_kernels/kernels/attention.py:69-170 walks all keys in one program).  For grids that
+ * leave most SMs idle in their last wave: 3 heads x 66 query blocks = 198 CTAs on 148 SMs run
+ * as two waves, 396 half-length CTAs as three half-waves.  n_ranks == 0: plain form, output o;
+ * n_ranks > 0: scatter form, o ignored.  part_o: fp32 scratch of k_splits*B*H*Lq*D elements,
+ * part_lse: fp32 scratch of k_splits*B*H*Lq elements (caller-owned, contents undefined
+ * afterwards).  k_splits == 1 is the ordinary kernel and needs no scratch.
+ */
+int fluxb_attention_split(const void* q, const void* k, const void* v, void* o, void* const* o_bases,
+                          int n_ranks, int64_t rows_per_rank, int64_t B, int64_t H, int64_t Lq, int64_t Lk,
+                          int64_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh,
+                          int64_t k_sl, int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
+                          int64_t o_sl, float sm_scale, int k_splits, float* part_o, float* part_lse,
+                          fluxb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -346,6 +346,30 @@ def test_attention_different_kv_length_and_strided_output(tk):
     assert float(out[:, :, H * D :].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("B,H,Lq,Lk,D,splits", [(1, 3, 1024, 2048, 128, 2), (2, 2, 300, 1100, 128, 3), (1, 4, 512, 1024, 64, 2)])
+def test_attention_key_splits(tk, B, H, Lq, Lk, D, splits):
+    """The keys cut into ranges that run as separate CTAs, merged by their log-sum-exp: same
+    result as the one-pass kernel up to the merge's rounding."""
+    from triton_kernels_b200.kernels.attention import attention_into, key_splits_for
+
+    g = gen(29)
+    q = torch.randn(B, H, Lq, D, generator=g).to(BF)
+    k = (2 * torch.randn(B, H, Lk, D, generator=g)).to(BF)
+    v = torch.randn(B, H, Lk, D, generator=g).to(BF)
+    o1 = torch.zeros(B, H, Lq, D, dtype=BF, device="cuda")
+    o2 = torch.zeros_like(o1)
+    attention_into(q.cuda(), k.cuda(), v.cuda(), o1, D**-0.5)
+    attention_into(q.cuda(), k.cuda(), v.cuda(), o2, D**-0.5, k_splits=splits)
+    want = O.scaled_dot_product_attention(q.float(), k.float(), v.float())
+    torch.testing.assert_close(o2.float().cpu(), want, atol=1e-2, rtol=2e-2)
+    assert rel_l2(o2, want) < 1e-2
+    assert rel_l2(o2, o1.float().cpu()) < 4e-3
+    # 3 heads x 66 query blocks: two waves of whole CTAs or three half-waves
+    assert key_splits_for(1, 3, 16896, 16896, 128, 148) == 2
+    assert [key_splits_for(1, h, 16896, 16896, 128, 148) for h in (6, 12, 24)] == [1, 1, 1]
+    assert key_splits_for(1, 24, 4608, 4608, 128, 148) == 1
+
+
 def test_device_status_is_clean(tk):
     from triton_kernels_b200 import _lib
 

@@ -42,6 +42,56 @@ def test_qkv_prep_scatter_matches_group_layout(lib):
         assert torch.equal(bufs[gi], send[gi])
 
 
+@pytest.mark.parametrize("Lt,Li,P,n2", [(128, 256, 2, 0), (32, 136, 4, 0), (64, 2048, 8, 0), (0, 200, 2, 512)])
+def test_linear_qkv_grouped_scatter_matches_head_major_form(lib, Lt, Li, P, n2):
+    """The q|k|v projection whose epilogue stores every head group into a buffer of its own (the
+    sequence-parallel form, here with all "peers" in local memory) against the head-major form:
+    same kernel up to the stores, so the bits must agree.  Stream lengths that are not multiples
+    of 128 exist only in the scatter form; they are checked against the assembly kernel."""
+    from triton_kernels_b200 import _lib, ops
+    from triton_kernels_b200.kernels.linear import linear, linear_qkv_grouped_into
+
+    g = gen(73)
+    B, H, D, K = 1, 8, 128, 256
+    Hp, L = H // P, Lt + Li
+    C3 = 3 * H * D
+    lens = [n for n in (Lt, Li) if n > 0]
+    xs = [torch.randn(B, n, K, generator=g).to(BF).cuda() for n in lens]
+    ws = [(0.05 * torch.randn(C3 + n2, K, generator=g)).to(BF).cuda() for _ in lens]
+    bs = [(0.1 * torch.randn(C3 + n2, generator=g)).to(BF).cuda() for _ in lens]
+    qs = [(1 + 0.1 * torch.randn(D, generator=g)).to(BF).cuda() for _ in lens]
+    ks = [(1 + 0.1 * torch.randn(D, generator=g)).to(BF).cuda() for _ in lens]
+    pe = torch.randn(1, 1, L, D // 2, 2, 2, generator=g).cuda()
+    y2s = [torch.zeros(B * n, n2, dtype=BF, device="cuda") if n2 else None for n in lens]
+    row = 3 * Hp * D
+    bufs = [torch.zeros(B, L, 3, Hp, D, dtype=BF, device="cuda") for _ in range(P)]
+    bases = (c_void_p * P)(*[b.data_ptr() for b in bufs])
+    streams = [dict(x=x, w=w, b=b, q_scale=q_, k_scale=k_, y2=y2) for x, w, b, q_, k_, y2 in zip(xs, ws, bs, qs, ks, y2s)]
+    linear_qkv_grouped_into(streams, pe, None, eps=1e-6, epi2=_lib.EPI_GELU,
+                            scatter=dict(bases=bases, n_groups=P, k_off=Hp * D, v_off=2 * Hp * D,
+                                         strides=(L * row, D, row), num_heads=H, head_dim=D))
+    torch.cuda.synchronize()
+    got = torch.stack(bufs, 0)  # [P, B, L, 3, Hp, D]
+    got = got.permute(3, 1, 0, 4, 2, 5).reshape(3, B, H, L, D)
+    if all(n % 128 == 0 for n in lens):
+        want = torch.zeros(3, B, H, L, D, dtype=BF, device="cuda")
+        y2w = [torch.zeros_like(y) if y is not None else None for y in y2s]
+        linear_qkv_grouped_into([dict(s_, y2=y) for s_, y in zip(streams, y2w)], pe, want, eps=1e-6, epi2=_lib.EPI_GELU)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    else:
+        qkvs = [linear(x, w[:C3], b[:C3]) for x, w, b in zip(xs, ws, bs)]
+        q, k, v = ops.qkv_prepare(qkvs, H, qs, ks, pe)
+        torch.cuda.synchronize()
+        assert torch.equal(got[2], v)
+        torch.testing.assert_close(got[0].float(), q.float(), atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(got[1].float(), k.float(), atol=2e-2, rtol=2e-2)
+    if n2:
+        for x, w, b, y2 in zip(xs, ws, bs, y2s):
+            ref = linear(x, w[C3:], b[C3:], activation="GELU").view(-1, n2)
+            torch.testing.assert_close(y2.float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_attention_scatter_matches_plain(lib):
     from triton_kernels_b200.kernels.attention import attention_into, attention_scatter_into
 
@@ -57,6 +107,13 @@ def test_attention_scatter_matches_plain(lib):
     torch.cuda.synchronize()
     for r in range(P):
         assert torch.equal(outs[r], want[:, r * L_loc:(r + 1) * L_loc])
+    # the key-split form of the same launch: the merge pass does the scatter
+    outs2 = [torch.zeros(B, L_loc, H * D, dtype=BF, device="cuda") for _ in range(P)]
+    bases2 = (c_void_p * P)(*[o.data_ptr() for o in outs2])
+    attention_scatter_into(q, k, v, bases2, P, L_loc, (L_loc * H * D, D, H * D), D**-0.5, k_splits=2)
+    torch.cuda.synchronize()
+    for r in range(P):
+        torch.testing.assert_close(outs2[r].float(), outs[r].float(), atol=1e-2, rtol=2e-2)
 
 
 def test_scatter_argument_validation(lib):

@@ -1,7 +1,8 @@
 """Ulysses sequence parallelism on real GPUs (needs at least two): each rank's shard of the
 sequence-parallel block output equals the corresponding rows of the single-GPU block output.
 Both exchanges are run: the two NCCL all-to-alls, and the peer-memory form in which the
-producing kernels store straight into the other GPU's arena.  Ranks are child processes over
+producing kernels store straight into the other GPU's arena (with the assembly kernel and with
+the q|k|v projection's own epilogue as the producer).  Ranks are child processes over
 NCCL with NVLS switched off; a rank only leaves between steps, after a collective teardown."""
 import os
 import socket
@@ -62,8 +63,8 @@ def _rank_main(rank: int, world: int, port: int, q_out):
                 return float((a.float() - b.float()).norm() / b.float().norm())
 
             errs = []
-            for exchange in ("nccl", "peer"):
-                sp = SequenceParallel(exchange=exchange)
+            for exchange, from_projection in (("nccl", False), ("peer", False), ("peer", True)):
+                sp = SequenceParallel(exchange=exchange, scatter_from_projection=from_projection)
                 dblk.sequence_parallel = sblk.sequence_parallel = sp
                 for _ in range(3):  # several rounds: the arenas and their epochs are reused
                     got_img, got_txt = dblk(img_l, txt_l, vec, pe_l)

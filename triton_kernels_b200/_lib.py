@@ -46,6 +46,8 @@ SIGNATURES = {
     "fluxb_linear": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P, _L, _L, _I, _P, _L, _P, _L, _L, _I, _P]),
     "fluxb_linear_grouped": (_I, [POINTER(LinearProblem), _I, _L, _L, _I, _L, _I, _I, _P]),
     "fluxb_linear_qkv_grouped": (_I, [POINTER(LinearProblem), POINTER(QkvStream), _I, _L, _L, _L, _L, _L, _P, _F, _L, _I, _I, _P]),
+    "fluxb_linear_qkv_grouped_scatter": (_I, [POINTER(LinearProblem), POINTER(QkvStream), _I, _L, _L, _L, _L, _L,
+                                              POINTER(c_void_p), _I, _L, _L, _L, _L, _L, _F, _L, _I, _I, _P]),
     "fluxb_modulation_gemv": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _P]),
     "fluxb_attention": (_I, [_P, _P, _P, _P] + [_L] * 5 + [_L] * 12 + [_F, _P]),
     "fluxb_layer_norm_modulation": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _F, _I, _P]),
@@ -69,6 +71,7 @@ SIGNATURES = {
     "fluxb_peer_wait": (_I, [POINTER(c_void_p), _I, _I, _I, _P]),
     "fluxb_qkv_prep_scatter": (_I, [_P, _L, _L, _P, _P, _P, _L, _L, _P, _P, _P, POINTER(c_void_p), _I, _L, _L,
                                     _L, _L, _L, _L, _L, _L, _L, _F, _P]),
+    "fluxb_attention_split": (_I, [_P, _P, _P, _P, POINTER(c_void_p), _I, _L] + [_L] * 5 + [_L] * 12 + [_F, _I, _P, _P, _P]),
     "fluxb_attention_scatter": (_I, [_P, _P, _P, POINTER(c_void_p), _I, _L] + [_L] * 5 + [_L] * 12 + [_F, _P]),
 }
 

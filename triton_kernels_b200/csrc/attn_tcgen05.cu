@@ -47,6 +47,13 @@ struct Params {
   // may be other GPUs' memory (plain stores only).
   int rows_per_rank;
   __nv_bfloat16* o_rank[8];
+  // Key-split form (k_splits > 1): CTA blockIdx.x handles query block blockIdx.x / k_splits and
+  // the key tiles of split blockIdx.x % k_splits; it writes its normalised partial output as fp32
+  // to part_o[split][batch][head][row][D] and the row's log2-sum-exp to part_lse[split][batch][head][row];
+  // merge_splits_kernel combines the splits and stores the final rows (plain or scatter form).
+  int k_splits;
+  float* part_o;
+  float* part_lse;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -138,10 +145,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * (2 * BQ);
+  const int split = p.k_splits > 1 ? (int)(blockIdx.x % p.k_splits) : 0;
+  const int q0 = (p.k_splits > 1 ? (int)(blockIdx.x / p.k_splits) : (int)blockIdx.x) * (2 * BQ);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
-  const int n_kv = (p.Lk + BKV - 1) / BKV;
+  const int n_kv_all = (p.Lk + BKV - 1) / BKV;
+  const int per_split = (n_kv_all + p.k_splits - 1) / p.k_splits;
+  const int j_first = split * per_split;  // first key tile of this CTA (0 without a split)
+  const int n_kv = min(n_kv_all - j_first, per_split);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -190,7 +201,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         uint8_t* dst = kv_smem + slot * TILE_BYTES;
         mbar_expect_tx(&kv_full[slot], TILE_BYTES);
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
-        const int row0 = (i >> 1) * BKV;
+        const int row0 = (j_first + (i >> 1)) * BKV;
         for (int hf = 0; hf < D / 64; ++hf)
           tma_load_4d(dst + hf * HALF_BYTES, tm, &kv_full[slot], hf * 64, row0, head, batch);
       }
@@ -307,7 +318,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       for (int c = 0; c < 4; ++c) tmem_ld_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
       tmem_wait_ld();
 
-      const int valid = p.Lk - j * BKV;  // keys of this tile that exist
+      const int valid = p.Lk - (j_first + j) * BKV;  // keys of this tile that exist
       if (valid < BKV) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
@@ -375,6 +386,25 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (ok && mbar_wait(&s_full[t], n_kv & 1, abort_flag, p.status, 32)) {
       tc_fence_after_sync();
       const float inv = 1.0f / l;
+      if (p.k_splits > 1) {
+        // partial result of this key range: normalised fp32 row + log2 of its sum of exponentials
+        const int64_t prow = ((static_cast<int64_t>(split) * gridDim.z + batch) * gridDim.y + head) * p.Lq + row;
+        if (row < p.Lq) p.part_lse[prow] = m_used + log2f(l);
+        float* prow_o = p.part_o + prow * D;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(o_addr + c * 32, o);
+          tmem_wait_ld();
+          if (row < p.Lq) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<float4*>(prow_o + c * 32 + g * 4) =
+                  make_float4(__uint_as_float(o[g * 4 + 0]) * inv, __uint_as_float(o[g * 4 + 1]) * inv,
+                              __uint_as_float(o[g * 4 + 2]) * inv, __uint_as_float(o[g * 4 + 3]) * inv);
+          }
+        }
+      } else {
       __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + (int64_t)row * p.o_sl;
       if (p.rows_per_rank > 0 && row < p.Lq) {
         const int owner = row / p.rows_per_rank;
@@ -397,6 +427,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           }
         }
       }
+      }
     }
   }
 
@@ -405,6 +436,50 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Combines the partial results of a key-split launch: for every (batch, head, row) the splits'
+// rows are weighted with exp2(lse_s - max lse) and normalised, then stored like the attention
+// kernel stores its rows (plain or scatter form).  One warp per (batch, head, row); a lane owns
+// D/32 consecutive output columns.
+template <int kD>
+__global__ void __launch_bounds__(256)
+merge_splits_kernel(const Params p, int B, int H) {
+  const int lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t items = static_cast<int64_t>(B) * H * p.Lq;
+  if (item >= items) return;
+  const int row = static_cast<int>(item % p.Lq);
+  const int head = static_cast<int>((item / p.Lq) % H);
+  const int batch = static_cast<int>(item / (static_cast<int64_t>(p.Lq) * H));
+  constexpr int PER = kD / 32;
+  float mx = -INFINITY;
+  for (int s_ = 0; s_ < p.k_splits; ++s_) mx = fmaxf(mx, p.part_lse[s_ * items + item]);
+  float acc[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+  float wsum = 0.f;
+  for (int s_ = 0; s_ < p.k_splits; ++s_) {
+    const float w = exp2f(p.part_lse[s_ * items + item] - mx);
+    wsum += w;
+    const float* src = p.part_o + (s_ * items + item) * kD + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] += w * src[i];
+  }
+  const float inv = 1.0f / wsum;
+  __nv_bfloat16* orow = p.o + batch * p.o_sb + head * p.o_sh + static_cast<int64_t>(row) * p.o_sl;
+  if (p.rows_per_rank > 0) {
+    const int owner = row / p.rows_per_rank;
+    orow = p.o_rank[owner] + batch * p.o_sb + head * p.o_sh + static_cast<int64_t>(row - owner * p.rows_per_rank) * p.o_sl;
+  }
+  if (PER == 4) {
+    uint2 w;
+    w.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    w.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    *reinterpret_cast<uint2*>(orow + lane * 4) = w;
+  } else {
+    *reinterpret_cast<uint32_t*>(orow + lane * 2) = pack_bf16(acc[0] * inv, acc[1] * inv);
   }
 }
 
@@ -429,7 +504,8 @@ static int attention_impl(const void* q, const void* k, const void* v, void* o, 
                           int64_t q_sh, int64_t q_sl, int64_t k_sb, int64_t k_sh, int64_t k_sl,
                           int64_t v_sb, int64_t v_sh, int64_t v_sl, int64_t o_sb, int64_t o_sh,
                           int64_t o_sl, float sm_scale, void* const* o_bases, int n_ranks,
-                          int64_t rows_per_rank, fluxb_stream_t stream) {
+                          int64_t rows_per_rank, fluxb_stream_t stream, int k_splits = 1,
+                          float* part_o = nullptr, float* part_lse = nullptr) {
   using namespace fluxb::attn;
   if (n_ranks > 0) {
     if (n_ranks > 8 || !o_bases || rows_per_rank <= 0 || rows_per_rank * n_ranks < Lq || rows_per_rank > (1 << 30))
@@ -472,6 +548,20 @@ static int attention_impl(const void* q, const void* k, const void* v, void* o, 
   p.v_lbo = HALF_BYTES;
   p.v_sbo = 1024;
   p.status = device_status_ptr();
+  if (k_splits < 1 || k_splits > 8) return set_error(FLUXB_ERR_BAD_ARG, "attention: 1..8 key splits");
+  if (k_splits > 1) {
+    if (!part_o || !part_lse || (reinterpret_cast<uintptr_t>(part_o) & 15))
+      return set_error(FLUXB_ERR_BAD_ARG, "attention: key splits need fp32 scratch for the partial rows and their log-sum-exp");
+    const int64_t tiles = (Lk + BKV - 1) / BKV, per = (tiles + k_splits - 1) / k_splits;
+    if ((k_splits - 1) * per >= tiles)
+      return set_error(FLUXB_ERR_BAD_ARG, "attention: %d key splits leave one without key tiles (%lld tiles)", k_splits,
+                       (long long)tiles);
+    if (((Lq + 2 * BQ - 1) / (2 * BQ)) * k_splits > (1ll << 30))
+      return set_error(FLUXB_ERR_UNSUPPORTED, "attention: dimension too large");
+  }
+  p.k_splits = k_splits;
+  p.part_o = part_o;
+  p.part_lse = part_lse;
   p.rows_per_rank = n_ranks > 0 ? (int)rows_per_rank : 0;
   for (int i = 0; i < 8; ++i) p.o_rank[i] = i < n_ranks ? static_cast<__nv_bfloat16*>(o_bases[i]) : nullptr;
 
@@ -480,8 +570,13 @@ static int attention_impl(const void* q, const void* k, const void* v, void* o, 
   const int smem = smem_bytes((int)D);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: cannot set shared memory size: %s", cudaGetErrorString(e));
-  dim3 grid((unsigned)((Lq + 2 * BQ - 1) / (2 * BQ)), (unsigned)H, (unsigned)B);
+  dim3 grid((unsigned)(((Lq + 2 * BQ - 1) / (2 * BQ)) * k_splits), (unsigned)H, (unsigned)B);
   kern<<<grid, THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, p);
+  if (k_splits > 1) {
+    const int64_t items = B * H * Lq;
+    auto merge = D == 128 ? merge_splits_kernel<128> : merge_splits_kernel<64>;
+    merge<<<(unsigned)((items + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p, (int)B, (int)H);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "attention: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
@@ -505,4 +600,16 @@ extern "C" int fluxb_attention_scatter(const void* q, const void* k, const void*
   if (n_ranks <= 0) return set_error(FLUXB_ERR_BAD_ARG, "attention_scatter: no output bases");
   return attention_impl(q, k, v, nullptr, B, H, Lq, Lk, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, v_sb, v_sh, v_sl,
                         o_sb, o_sh, o_sl, sm_scale, o_bases, n_ranks, rows_per_rank, stream);
+}
+
+extern "C" int fluxb_attention_split(const void* q, const void* k, const void* v, void* o, void* const* o_bases,
+                                     int n_ranks, int64_t rows_per_rank, int64_t B, int64_t H, int64_t Lq,
+                                     int64_t Lk, int64_t D, int64_t q_sb, int64_t q_sh, int64_t q_sl, int64_t k_sb,
+                                     int64_t k_sh, int64_t k_sl, int64_t v_sb, int64_t v_sh, int64_t v_sl,
+                                     int64_t o_sb, int64_t o_sh, int64_t o_sl, float sm_scale, int k_splits,
+                                     float* part_o, float* part_lse, fluxb_stream_t stream) {
+  if (n_ranks < 0) return set_error(FLUXB_ERR_BAD_ARG, "attention_split: negative rank count");
+  return attention_impl(q, k, v, n_ranks > 0 ? nullptr : o, B, H, Lq, Lk, D, q_sb, q_sh, q_sl, k_sb, k_sh, k_sl, v_sb,
+                        v_sh, v_sl, o_sb, o_sh, o_sl, sm_scale, n_ranks > 0 ? o_bases : nullptr, n_ranks, rows_per_rank,
+                        stream, k_splits, part_o, part_lse);
 }

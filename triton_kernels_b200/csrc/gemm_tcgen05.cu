@@ -59,6 +59,12 @@ struct Params {
   const __nv_bfloat16* qk_scale[2];    // [128] each
   int row_offset, heads, l_total;      // joint position of this problem's first token
   float eps;
+  // Scatter form of EPI_QKV_HEADS (scat_groups > 0): head h of q goes to
+  // scat_base[h / scat_hpg] + b*scat_sb + (h % scat_hpg)*scat_sh + l*scat_sl, k and v scat_koff /
+  // scat_voff elements further; the bases may be other GPUs' memory (plain 16-byte stores only).
+  __nv_bfloat16* scat_base[8];
+  int scat_groups, scat_hpg;
+  int64_t scat_sb, scat_sh, scat_sl, scat_koff, scat_voff;
 };
 constexpr int EPI_QKV_HEADS = 3;  // internal epilogue code, set by fluxb_linear_qkv_grouped
 
@@ -324,6 +330,8 @@ struct Grouped {
   int pair_stages;
 };
 
+static_assert(sizeof(Grouped) <= 4096, "kernel parameters are limited to 4 KB");
+
 __device__ __forceinline__ int find_problem(const Grouped& g, int tile) {
   int i = 0;
 #pragma unroll
@@ -359,11 +367,13 @@ __device__ __forceinline__ void qkv_load16(const Params& p, uint32_t taddr, int 
   for (int e = 0; e < 16; ++e) x[e] = __bfloat162float(__float2bfloat16_rn(x[e]));
 }
 
+template <bool kScatter>
 __device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtensorMap* tm, uint32_t t_addr, int part,
                                                   int head0, int n0, int heads_in_tile, int b, int l0, int r_local,
-                                                  bool rows_ok, uint8_t* out_stage, int eg, bool store_issuer) {
+                                                  bool rows_ok, uint8_t* out_stage, int eg, bool store_issuer,
+                                                  int rows_left) {
   const __nv_bfloat16* w = part < 2 ? p.qk_scale[part] : nullptr;
-  const bool rotate = part < 2 && p.pe != nullptr && rows_ok;
+  const bool rotate = part < 2 && p.pe != nullptr && rows_ok && (!kScatter || r_local < rows_left);
   float rstd0 = 1.f, rstd1 = 1.f;
   if (w != nullptr) {
 #pragma unroll 1
@@ -444,6 +454,33 @@ __device__ __forceinline__ void qkv_tile_epilogue(const Params& p, const CUtenso
     if ((it & 1) == 1) {
       fence_proxy_async_smem();
       asm volatile("bar.sync 3, 256;" ::: "memory");
+      if (kScatter) {
+        // All 256 epilogue threads copy the finished staging tiles out with plain 16-byte stores:
+        // eight consecutive threads write one row's 128 bytes of one head.  The destination of a
+        // head depends on its group (another GPU's arena under sequence parallelism), and rows
+        // beyond the stream's end are skipped one by one, so stream lengths need not be
+        // multiples of 128 here.  The barrier at the top of the next piece orders these reads
+        // before the tiles are written again.
+        const int tid = eg * 128 + r_local;
+        const int64_t part_off = part == 0 ? 0 : (part == 1 ? p.scat_koff : p.scat_voff);
+#pragma unroll 1
+        for (int hh = 0; hh < heads_in_tile; ++hh) {
+          const int head = head0 + hh;
+          const int grp = head / p.scat_hpg;
+          __nv_bfloat16* dst_head = p.scat_base[grp] + part_off + b * p.scat_sb + (head - grp * p.scat_hpg) * p.scat_sh +
+                                    piece * 64;
+          const uint8_t* src_tile = out_stage + hh * OUT_BUF_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int idx = tid + 256 * k;
+            const int r = idx >> 3, q = idx & 7;
+            if (r < rows_left) {
+              const uint4 v = *reinterpret_cast<const uint4*>(src_tile + r * 128 + ((q ^ (r & 7)) << 4));
+              *reinterpret_cast<uint4*>(dst_head + (int64_t)(l0 + r) * p.scat_sl + q * 8) = v;
+            }
+          }
+        }
+      } else
       // group eg's issuer stores staging tile eg = head eg of the tile
       if (store_issuer && rows_ok && eg < heads_in_tile) {
         asm volatile(
@@ -605,7 +642,7 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
       // The tile leaves in four 64-column pieces: registers -> swizzled staging tile in shared
       // memory -> one TMA store of full 128-byte lines.  (Storing 16 bytes per thread straight
       // to global memory, 32 different rows per warp instruction, cost 9 % of the GEMM.)
-      if (kMode == 1 && !second) {
+      if (kMode >= 1 && !second) {
         const int hd = p.heads * 128;
         const int part = n0 / hd;
         const int head0 = (n0 - part * hd) / 128;
@@ -613,8 +650,8 @@ gemm_pair_kernel(const __grid_constant__ Grouped g) {
         const int b = row0 / (int)p.rows_per_batch;
         const int l0 = p.row_offset + (row0 - b * (int)p.rows_per_batch);
         const int heads_in_tile = (p.split - n0) >= BN ? BN / 128 : (p.split - n0) / 128;  // split = 3*heads*128
-        qkv_tile_epilogue(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok, out_stage, eg,
-                          store_issuer);
+        qkv_tile_epilogue<kMode == 2>(p, &pr.tm_y, t_addr, part, head0, n0, heads_in_tile, b, l0, r_local, rows_ok,
+                                      out_stage, eg, store_issuer, p.M - row0);
       } else {
       // ordinary columns: this group's two pieces, through its own staging tile
       uint8_t* buf = out_stage + eg * OUT_BUF_BYTES;
@@ -735,6 +772,8 @@ static int prepare_problem(const fluxb_linear_problem& a, int64_t N, int64_t K, 
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.status = device_status_ptr();
   p.pe = nullptr; p.qk_scale[0] = p.qk_scale[1] = nullptr; p.row_offset = 0; p.heads = 0; p.l_total = 0; p.eps = 0.f;
+  p.scat_groups = 0; p.scat_hpg = 1; p.scat_sb = p.scat_sh = p.scat_sl = p.scat_koff = p.scat_voff = 0;
+  for (int gi = 0; gi < 8; ++gi) p.scat_base[gi] = nullptr;
   p.pair_stages = fluxb::gemm2::STAGES;
   {
     // Keep the smaller operand resident in L2 when it fits, sweep the larger one.
@@ -819,10 +858,16 @@ extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int co
   return FLUXB_OK;
 }
 
-extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
-                                        int count, int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K,
-                                        void* qkv_out, float eps, int64_t N2, int epi2, int round_before_act,
-                                        fluxb_stream_t stream) {
+struct QkvScatter {  // destination of the scatter form, see fluxb_linear_qkv_grouped_scatter
+  void* const* bases;
+  int n_groups;
+  int64_t k_off, v_off, sb, sh, sl;
+};
+
+static int linear_qkv_grouped_impl(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
+                                   int count, int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K,
+                                   void* qkv_out, const QkvScatter* scat, float eps, int64_t N2, int epi2,
+                                   int round_before_act, fluxb_stream_t stream) {
   using namespace fluxb::gemm;
   if (count < 1 || count > fluxb::gemm2::MAX_PROBLEMS || !problems || !streams)
     return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: 1..%d problems with their stream descriptions", fluxb::gemm2::MAX_PROBLEMS);
@@ -834,7 +879,17 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: %lld heads (the head count must be even)", (long long)H);
   if (B <= 0 || H <= 0 || L_total <= 0 || K <= 0 || B > 65535 || H > 65535 || L_total > (1 << 30))
     return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: bad sizes");
-  if (!qkv_out || !aligned16(qkv_out)) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: output null or misaligned");
+  if (scat == nullptr) {
+    if (!qkv_out || !aligned16(qkv_out)) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: output null or misaligned");
+  } else {
+    if (scat->n_groups < 1 || scat->n_groups > 8 || !scat->bases || H % scat->n_groups)
+      return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped_scatter: 1..8 head groups that divide the head count");
+    for (int i = 0; i < scat->n_groups; ++i)
+      if (!scat->bases[i] || !aligned16(scat->bases[i]))
+        return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped_scatter: output base %d is null or misaligned", i);
+    if (scat->k_off % 8 || scat->v_off % 8 || scat->sb % 8 || scat->sh % 8 || scat->sl % 8 || scat->sl < D)
+      return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped_scatter: offsets and strides must be multiples of 8 elements");
+  }
   if (N2 < 0 || N2 % 8) return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: N2 must be a non-negative multiple of 8");
   if (epi2 != FLUXB_EPI_NONE && epi2 != FLUXB_EPI_GELU)
     return set_error(FLUXB_ERR_UNSUPPORTED, "linear_qkv_grouped: the extra columns take no epilogue or GELU");
@@ -847,7 +902,7 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
   g.pair_stages = fluxb::gemm2::STAGES;
   // one 5-D map over [3, B, H, L_total, D] for all problems
   CUtensorMap tm_out;
-  {
+  if (scat == nullptr) {
     const uint64_t dims[5] = {(uint64_t)D, (uint64_t)L_total, (uint64_t)H, (uint64_t)B, 3};
     const uint64_t strides[4] = {(uint64_t)D * 2, (uint64_t)L_total * D * 2, (uint64_t)H * L_total * D * 2,
                                  (uint64_t)B * H * L_total * D * 2};
@@ -859,14 +914,17 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     fluxb_linear_problem a = problems[i];
     const fluxb_qkv_stream& sdesc = streams[i];
     const int64_t Ls = a.rows_per_batch;
-    if (a.M <= 0 || Ls <= 0 || a.M != B * Ls || Ls % 128)
+    // The head-major form leaves through 128-row TMA boxes; the scatter form masks row by row, so
+    // with one batch item any stream length and offset will do.
+    const int64_t align = (scat != nullptr && B == 1) ? 1 : 128;
+    if (a.M <= 0 || Ls <= 0 || a.M != B * Ls || Ls % align)
       return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: each stream needs M = B * rows_per_batch with rows_per_batch a multiple of 128");
-    if (sdesc.row_offset < 0 || sdesc.row_offset % 128 || sdesc.row_offset + Ls > L_total)
+    if (sdesc.row_offset < 0 || sdesc.row_offset % align || sdesc.row_offset + Ls > L_total)
       return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: row_offset must be a multiple of 128 inside the joint sequence");
     if ((sdesc.q_scale == nullptr) != (sdesc.k_scale == nullptr) || !aligned16(sdesc.q_scale) || !aligned16(sdesc.k_scale) ||
         !aligned16(sdesc.pe))
       return set_error(FLUXB_ERR_BAD_ARG, "linear_qkv_grouped: scales go together; scales and pe must be 16-byte aligned");
-    a.y = qkv_out; a.ldy = D;  // the q|k|v columns leave through the 5-D map only
+    a.y = scat == nullptr ? qkv_out : scat->bases[0]; a.ldy = D;  // the q|k|v columns do not leave through y
     a.resid = nullptr; a.gate = nullptr;
     if (N2 == 0) a.y2 = nullptr;
     fluxb::gemm2::Problem& pr = g.prob[g.count];
@@ -881,6 +939,14 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     pr.p.heads = (int)H;
     pr.p.l_total = (int)L_total;
     pr.p.eps = eps;
+    if (scat != nullptr) {
+      pr.p.scat_groups = scat->n_groups;
+      pr.p.scat_hpg = (int)(H / scat->n_groups);
+      for (int gi = 0; gi < 8; ++gi) pr.p.scat_base[gi] = gi < scat->n_groups ? static_cast<__nv_bfloat16*>(scat->bases[gi]) : nullptr;
+      pr.p.scat_sb = scat->sb; pr.p.scat_sh = scat->sh; pr.p.scat_sl = scat->sl;
+      pr.p.scat_koff = scat->k_off; pr.p.scat_voff = scat->v_off;
+      tm_out = pr.tm_a;  // never used for a store in this form; any valid map will do for the prefetch
+    }
     pr.tm_y = tm_out;
     pr.tm_y2 = tm_out;
     if (N2 > 0) {  // extra columns [3*H*D, 3*H*D + N2): an ordinary output with epilogue epi2
@@ -895,14 +961,32 @@ extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, co
     g.total_tiles += pr.tiles_m * pr.p.tiles_n;
     ++g.count;
   }
-  cudaError_t e = cudaFuncSetAttribute(fluxb::gemm2::gemm_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       fluxb::gemm2::SMEM_BYTES);
+  auto kern = scat == nullptr ? fluxb::gemm2::gemm_pair_kernel<1> : fluxb::gemm2::gemm_pair_kernel<2>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, fluxb::gemm2::SMEM_BYTES);
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear_qkv_grouped: cannot set shared memory size: %s", cudaGetErrorString(e));
   const int pairs = g.total_tiles < sm_count() / 2 ? g.total_tiles : sm_count() / 2;
-  fluxb::gemm2::gemm_pair_kernel<1><<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
+  kern<<<2 * pairs, fluxb::gemm2::THREADS, fluxb::gemm2::SMEM_BYTES, st>>>(g);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(FLUXB_ERR_CUDA, "linear_qkv_grouped: launch failed: %s", cudaGetErrorString(e));
   return FLUXB_OK;
+}
+
+extern "C" int fluxb_linear_qkv_grouped(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
+                                        int count, int64_t B, int64_t H, int64_t D, int64_t L_total, int64_t K,
+                                        void* qkv_out, float eps, int64_t N2, int epi2, int round_before_act,
+                                        fluxb_stream_t stream) {
+  return linear_qkv_grouped_impl(problems, streams, count, B, H, D, L_total, K, qkv_out, nullptr, eps, N2, epi2,
+                                 round_before_act, stream);
+}
+
+extern "C" int fluxb_linear_qkv_grouped_scatter(const fluxb_linear_problem* problems, const fluxb_qkv_stream* streams,
+                                                int count, int64_t B, int64_t H, int64_t D, int64_t L_total,
+                                                int64_t K, void* const* group_bases, int n_groups, int64_t k_off,
+                                                int64_t v_off, int64_t o_sb, int64_t o_sh, int64_t o_sl, float eps,
+                                                int64_t N2, int epi2, int round_before_act, fluxb_stream_t stream) {
+  const QkvScatter scat{group_bases, n_groups, k_off, v_off, o_sb, o_sh, o_sl};
+  return linear_qkv_grouped_impl(problems, streams, count, B, H, D, L_total, K, nullptr, &scat, eps, N2, epi2,
+                                 round_before_act, stream);
 }
 
 extern "C" int fluxb_linear(const void* x, const void* w, const void* bias, void* y, int64_t M,

@@ -94,8 +94,19 @@ def qkv_projection_supported(stream_lengths, head_dim: int, num_heads: int) -> b
             and all(L > 0 and L % 128 == 0 for L in stream_lengths))
 
 
-def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_out: torch.Tensor, eps: float = 1e-6,
-                            epi2: int = _lib.EPI_NONE, round_before_act: bool = False) -> None:
+def qkv_projection_scatter_supported(stream_lengths, head_dim: int, num_heads: int, batch: int) -> bool:
+    """Whether linear_qkv_grouped_into takes these streams in its scatter form (one output base per
+    head group, rows masked one by one): with one batch item any stream lengths will do."""
+    import os
+
+    if os.environ.get("FLUXB_GEMM_PAIR", "1") == "0":
+        return False
+    return (head_dim == 128 and num_heads % 2 == 0 and 1 <= len(stream_lengths) <= 4
+            and all(L > 0 and (batch == 1 or L % 128 == 0) for L in stream_lengths))
+
+
+def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_out: torch.Tensor | None, eps: float = 1e-6,
+                            epi2: int = _lib.EPI_NONE, round_before_act: bool = False, scatter: dict | None = None) -> None:
     """q|k|v projections of up to four token streams with the whole path to attention in the GEMM
     epilogue (fluxb_linear_qkv_grouped): per-head RMS norm of q and k, rotation with `pe`,
     head-major layout, streams concatenated in list order.
@@ -104,9 +115,20 @@ def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_ou
     k_scale [D] or None); every L_i a multiple of 128.  pe: fp32 [1, 1, L, D/2, 2, 2] over the joint
     sequence or None.  qkv_out: bf16 [3, B, H, L, D] contiguous with L = sum L_i, D = 128.
     A stream may carry `y2` ([B*L_i, N2] view, unit column stride): then w (and b) have N2 more rows
-    after the q|k|v ones and those columns go to y2 with epilogue `epi2` (none or GELU)."""
-    three, B, H, L, D = qkv_out.shape
-    assert three == 3 and qkv_out.is_contiguous() and qkv_out.dtype == torch.bfloat16
+    after the q|k|v ones and those columns go to y2 with epilogue `epi2` (none or GELU).
+
+    Scatter form (fluxb_linear_qkv_grouped_scatter; qkv_out = None): `scatter` = dict(bases = ctypes
+    array of n_groups device pointers, n_groups, k_off, v_off, strides = (batch, head, token) in
+    elements, num_heads, head_dim): head h of q, token l, lands at bases[h // (H/n_groups)] +
+    b*sb + (h % (H/n_groups))*sh + l*sl, k and v k_off / v_off elements further; the bases may lie
+    in other GPUs' memory.  Stream lengths are free when B == 1."""
+    if scatter is None:
+        three, B, H, L, D = qkv_out.shape
+        assert three == 3 and qkv_out.is_contiguous() and qkv_out.dtype == torch.bfloat16
+    else:
+        assert qkv_out is None
+        B, H, D = streams[0]["x"].shape[0], scatter["num_heads"], scatter["head_dim"]
+        L = sum(s["x"].shape[1] for s in streams)
     assert sum(s["x"].shape[1] for s in streams) == L
     pe_c = None
     if pe is not None:
@@ -133,6 +155,14 @@ def linear_qkv_grouped_into(streams: list[dict], pe: torch.Tensor | None, qkv_ou
         slot.rows_per_batch = x.shape[1]
         d.pe, d.q_scale, d.k_scale, d.row_offset = _lib.ptr(pe_c), _lib.ptr(qs), _lib.ptr(ks), row
         row += x.shape[1]
+    if scatter is not None:
+        sb, sh, sl = scatter["strides"]
+        _lib.check(
+            _lib.load().fluxb_linear_qkv_grouped_scatter(
+                arr, desc, len(streams), B, H, D, L, K, scatter["bases"], scatter["n_groups"], scatter["k_off"],
+                scatter["v_off"], sb, sh, sl, eps, N2, epi2, int(round_before_act), _lib.stream_handle())
+        )
+        return
     _lib.check(
         _lib.load().fluxb_linear_qkv_grouped(arr, desc, len(streams), B, H, D, L, K, _lib.ptr(qkv_out), eps, N2, epi2,
                                              int(round_before_act), _lib.stream_handle())

@@ -28,12 +28,18 @@ import torch
 from torch import Tensor, nn
 
 from triton_kernels_b200 import _lib
-from triton_kernels_b200.kernels.attention import attention_into, attention_scatter_into, scaled_dot_product_attention
+from triton_kernels_b200.kernels.attention import (
+    attention_into,
+    attention_scatter_into,
+    key_splits_for,
+    scaled_dot_product_attention,
+)
 from triton_kernels_b200.kernels.linear import (
     linear,
     linear_grouped_into,
     linear_into,
     linear_qkv_grouped_into,
+    qkv_projection_scatter_supported,
     qkv_projection_supported,
 )
 from triton_kernels_b200.kernels.normalization import layer_norm_modulation_into
@@ -156,16 +162,7 @@ def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Ten
         args = [(s, n.query_norm.scale.to(dt), n.key_norm.scale.to(dt)) for s, n in streams]
         qkv_prepare_scatter(args, pe, pb.q_bases, pb.P, pb.k_off, pb.v_off, num_heads, D, pb.qkv_strides,
                             eps=1e-6)
-        pb.arena.signal(0)
-        pb.arena.wait(0)
-        qv, kv, vv = (pb.recv[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [B, Hp, L, D] views
-        attention_scatter_into(qv, kv, vv, pb.o_bases, pb.P, L_loc, pb.o_strides, scale)
-        pb.arena.signal(1)
-        pb.arena.wait(1)
-        if out is None:
-            return pb.out  # valid until this rank's next attention with the same shape
-        out.copy_(pb.out)
-        return out
+        return _peer_attention(pb, L_loc, scale, out)
     if out is None:
         out = torch.empty((B, L_loc, num_heads * D), device=dev, dtype=dt)
     shape, layout = sp.send_layout(B, L_loc, num_heads, D)
@@ -179,9 +176,32 @@ def _joint_attention(streams, pe: Tensor, num_heads: int, scale: float, out: Ten
     L = full.shape[1]
     o = torch.empty((B, L, Hp * D), device=dev, dtype=dt)
     qv, kv, vv = (full[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [B, Hp, L, D] views
-    attention_into(qv, kv, vv, o.view(B, L, Hp, D).permute(0, 2, 1, 3), scale)
+    attention_into(qv, kv, vv, o.view(B, L, Hp, D).permute(0, 2, 1, 3), scale, k_splits=key_splits_for(B, Hp, L, L, D))
     sp.heads_to_tokens(o, out)
     return out
+
+
+def _peer_attention(pb, L_loc: int, scale: float, out: Tensor | None) -> Tensor:
+    """Attention over the q/k/v that all ranks have stored into this rank's arena, for the local
+    heads, with the output rows stored straight into their owners' arenas.  Barrier 0: all q/k/v
+    have arrived; barrier 1: all outputs have arrived, and the peers may overwrite this rank's
+    receive buffer again."""
+    pb.arena.signal(0)
+    pb.arena.wait(0)
+    qv, kv, vv = (pb.recv[:, :, i].permute(0, 2, 1, 3) for i in range(3))  # [B, Hp, L, D] views
+    attention_scatter_into(qv, kv, vv, pb.o_bases, pb.P, L_loc, pb.o_strides, scale)
+    pb.arena.signal(1)
+    pb.arena.wait(1)
+    if out is None:
+        return pb.out  # valid until this rank's next attention with the same shape
+    out.copy_(pb.out)
+    return out
+
+
+def _scatter_target(pb, num_heads: int, head_dim: int) -> dict:
+    """Where the scatter form of the q|k|v projection writes: the peers' receive buffers."""
+    return dict(bases=pb.q_bases, n_groups=pb.P, k_off=pb.k_off, v_off=pb.v_off, strides=pb.qkv_strides,
+                num_heads=num_heads, head_dim=head_dim)
 
 
 def _ln_mod(x: Tensor, packed_mod: Tensor, chunk_shift: int) -> Tensor:
@@ -252,6 +272,19 @@ class SingleStreamBlock(nn.Module):
                 pe, qkv_heads, eps=1e-6, epi2=_lib.EPI_GELU)
             attention_into(qkv_heads[0], qkv_heads[1], qkv_heads[2],
                            cat[:, :, :C].unflatten(2, (H, D)).permute(0, 2, 1, 3), self.scale)
+            out = torch.empty_like(x)
+            _gated_linear(cat.view(B * L, C + M), self.linear2, x.view(B * L, C), mod[:, 2 * C : 3 * C], L, out.view(B * L, C))
+            return out
+        if (sp is not None and sp.world > 1 and sp.scatter_from_projection and self.fuse_qkv_epilogue
+                and qkv_projection_scatter_supported((L,), D, H, B) and (3 * C) % 256 == 0 and M % 8 == 0):
+            # sequence parallel: the q|k|v columns leave linear1 normalised and rotated, each head
+            # group straight into the arena of the rank that attends over it
+            pb = sp.peer_buffers(B, L, H, D, x.dtype)
+            linear_qkv_grouped_into(
+                [dict(x=x_mod, w=self.linear1.weight, b=self.linear1.bias, q_scale=self.norm.query_norm.scale,
+                      k_scale=self.norm.key_norm.scale, y2=cat.view(B * L, C + M)[:, C:])],
+                pe, None, eps=1e-6, epi2=_lib.EPI_GELU, scatter=_scatter_target(pb, H, D))
+            _peer_attention(pb, L, self.scale, cat[:, :, :C])
             out = torch.empty_like(x)
             _gated_linear(cat.view(B * L, C + M), self.linear2, x.view(B * L, C), mod[:, 2 * C : 3 * C], L, out.view(B * L, C))
             return out
@@ -342,6 +375,15 @@ class DoubleStreamBlock(nn.Module):
                 for h, a in zip(h1, attns)], pe, qkv_heads, eps=1e-6)
             attn = torch.empty((B, Lt + Li, C), device=dev, dtype=dt)
             attention_into(qkv_heads[0], qkv_heads[1], qkv_heads[2], attn.unflatten(2, (H, D)).permute(0, 2, 1, 3), D**-0.5)
+        elif (sp is not None and sp.world > 1 and sp.scatter_from_projection and self.fuse_qkv_epilogue
+              and qkv_projection_scatter_supported(Ls, D, H, B)):
+            # sequence parallel: the same epilogue, storing every head group straight into the arena
+            # of the rank that attends over it
+            pb = sp.peer_buffers(B, Lt + Li, H, D, dt)
+            linear_qkv_grouped_into([
+                dict(x=h, w=a.qkv.weight, b=a.qkv.bias, q_scale=a.norm.query_norm.scale, k_scale=a.norm.key_norm.scale)
+                for h, a in zip(h1, attns)], pe, None, eps=1e-6, scatter=_scatter_target(pb, H, D))
+            attn = _peer_attention(pb, Lt + Li, D**-0.5, None)
         else:
             # both streams' qkv projections in one launch, then the assembly kernel
             qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]

@@ -40,12 +40,19 @@ from torch import Tensor
 class SequenceParallel:
     """Process-group handle plus the two layout-changing exchanges."""
 
-    def __init__(self, group=None, exchange: str = "nccl"):
+    def __init__(self, group=None, exchange: str = "nccl", scatter_from_projection: bool = False):
+        """`scatter_from_projection` (peer exchange only): let the q|k|v projection's own epilogue
+        store every head group into its owner's arena (fluxb_linear_qkv_grouped_scatter) instead
+        of running the assembly kernel after the projection.  Off by default: with half of the
+        stores going over NVLink the GEMM's epilogue warps stall on them, and on two B200s the
+        block step took 3.57 ms against 3.48 ms with the separate assembly kernel, although the
+        same epilogue costs only 4-6 % of the GEMM when all destinations are local."""
         assert exchange in ("nccl", "peer")
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.exchange = exchange
+        self.scatter_from_projection = bool(scatter_from_projection) and exchange == "peer"
         self._peer: dict = {}
 
     # ---- peer-memory exchange ------------------------------------------------------------
