@@ -863,6 +863,18 @@ mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __re
                 const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
                 int K, int64_t b0, int apply_silu) {
   extern __shared__ float sv[];  // [BT][K]
+  // first chunk of this warp's first row: requested before act(vec) is staged, so that the
+  // weight stream starts with the kernel and not after the block's first barrier
+  const bool chunked = K % 1536 == 0;
+  uint4 cur[6];
+  if (chunked) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row < N) {
+#pragma unroll
+      for (int u = 0; u < 6; ++u)
+        cur[u] = __ldg(reinterpret_cast<const uint4*>(w + row * K + (threadIdx.x & 31) * 8 + u * 256));
+    }
+  }
   for (int i = threadIdx.x; i < BT * K; i += blockDim.x) {
     const int bb = i / K, kk = i % K;
     float t = __bfloat162float(vec[(b0 + bb) * K + kk]);
@@ -875,6 +887,59 @@ mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __re
   const int warps = blockDim.x >> 5;
   // A few persistent blocks per SM; every warp walks output columns with a grid stride, four
   // 16-byte weight loads in flight per lane.
+  if (chunked) {
+    // Rows that are whole multiples of 1536 elements (the Flux hidden size is two) are streamed
+    // as half-row chunks of six 16-byte loads per lane, and the loads of chunk i+1 are issued
+    // before chunk i is consumed: a warp always has a chunk in flight, across row boundaries too,
+    // where the form below drains its load queue between two rows.
+    const int cpr = K / 1536;
+    const int64_t stride = (int64_t)gridDim.x * warps;
+    int64_t row = (int64_t)blockIdx.x * warps + warp;
+    int ch = 0;
+    uint4 nxt[6];
+    float acc[BT];
+#pragma unroll
+    for (int bb = 0; bb < BT; ++bb) acc[bb] = 0.f;
+    while (row < N) {
+      const bool last = ch + 1 == cpr;
+      const int64_t nrow = last ? row + stride : row;
+      const int nch = last ? 0 : ch + 1;
+      if (nrow < N) {
+#pragma unroll
+        for (int u = 0; u < 6; ++u)
+          nxt[u] = __ldg(reinterpret_cast<const uint4*>(w + nrow * K + nch * 1536 + lane * 8 + u * 256));
+      }
+      const float* svc = sv + ch * 1536 + lane * 8;
+#pragma unroll
+      for (int u = 0; u < 6; ++u) {
+        Vec<__nv_bfloat16> wv;
+        wv.unpack(cur[u]);
+#pragma unroll
+        for (int bb = 0; bb < BT; ++bb) {
+          const float4 a0 = *reinterpret_cast<const float4*>(svc + bb * K + u * 256);
+          const float4 a1 = *reinterpret_cast<const float4*>(svc + bb * K + u * 256 + 4);
+          acc[bb] += wv.v[0] * a0.x + wv.v[1] * a0.y + wv.v[2] * a0.z + wv.v[3] * a0.w +
+                     wv.v[4] * a1.x + wv.v[5] * a1.y + wv.v[6] * a1.z + wv.v[7] * a1.w;
+        }
+      }
+      if (last) {
+#pragma unroll
+        for (int bb = 0; bb < BT; ++bb) {
+          const float sum = warp_sum(acc[bb]);
+          if (lane == 0) {
+            const float bv = bias != nullptr ? __bfloat162float(bias[row]) : 0.f;
+            out[(b0 + bb) * N + row] = __float2bfloat16_rn(sum + bv);
+          }
+          acc[bb] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 6; ++u) cur[u] = nxt[u];
+      row = nrow;
+      ch = nch;
+    }
+    return;
+  }
   for (int64_t n = (int64_t)blockIdx.x * warps + warp; n < N; n += (int64_t)gridDim.x * warps) {
     const __nv_bfloat16* wr = w + n * K;
     float acc[BT];
