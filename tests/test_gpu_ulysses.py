@@ -75,6 +75,36 @@ def _rank_main(rank: int, world: int, port: int, q_out):
                 torch.cuda.synchronize()
                 sp.check()  # raises if a flag wait of the peer exchange gave up
                 sp.close()
+            # A long sequence over few heads: 2 local heads x 80 query blocks = 160 CTAs leave the
+            # second wave of the attention launch almost empty, so both exchanges take the
+            # key-split form of attention (partial rows merged by their log-sum-exp, the merge
+            # pass doing the scatter store under the peer exchange).
+            from triton_kernels_b200.kernels.attention import key_splits_for
+
+            C2, H2, Lt2, gh2, gw2 = 512, 4, 512, 156, 128
+            assert key_splits_for(1, H2 // world, Lt2 + gh2 * gw2, Lt2 + gh2 * gw2) == 2
+            g2 = torch.Generator().manual_seed(42)
+            pd2 = {k: v.to(BF) for k, v in O.init_params(O.double_block_shapes(C2), g2, bias_std=0.02, scale_jitter=0.1).items()}
+            img2 = torch.randn(1, gh2 * gw2, C2, generator=g2).to(BF).cuda()
+            txt2 = torch.randn(1, Lt2, C2, generator=g2).to(BF).cuda()
+            vec2 = torch.randn(1, C2, generator=g2).to(BF).cuda()
+            pe2 = O.embed_nd(O.flux_position_ids(Lt2, gh2, gw2), [16, 56, 56]).cuda()
+            blk2 = tk.DoubleStreamBlock(C2, H2, 4.0).to(BF)
+            blk2.load_state_dict(pd2)
+            blk2 = blk2.cuda()
+            want_i2, want_t2 = blk2(img2, txt2, vec2, pe2)
+            txt2_l, img2_l, pe2_l = shard_joint_sequence(txt2, img2, pe2, rank, world)
+            ri = slice(rank * (gh2 * gw2 // world), (rank + 1) * (gh2 * gw2 // world))
+            rt = slice(rank * (Lt2 // world), (rank + 1) * (Lt2 // world))
+            for exchange in ("peer", "nccl"):
+                sp = SequenceParallel(exchange=exchange)
+                blk2.sequence_parallel = sp
+                for _ in range(2):
+                    got_i2, got_t2 = blk2(img2_l, txt2_l, vec2, pe2_l)
+                    errs += [rel(got_i2, want_i2[:, ri]), rel(got_t2, want_t2[:, rt])]
+                torch.cuda.synchronize()
+                sp.check()
+                sp.close()
         code, where = _lib.device_status()
         assert code == 0, f"device status {code} at {where}"
         dist.barrier()

@@ -276,16 +276,18 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (!wait(&kv_full[v_slot], (iv / KV_SLOTS) & 1, 23)) { ok = false; break; }
         const int ik = 2 * j + 2;
         const int k_slot = ik % KV_SLOTS;
+        // The next K tile is waited for here, while this warp would be idle anyway until the
+        // probabilities arrive, not between P.V and Q.K^T where the wait would sit on the chain
+        // scores -> probabilities -> P.V -> next scores of a query tile.  (Its slot was freed an
+        // iteration ago, so the load does not depend on anything issued below.)  K and V come
+        // through TMA, the same proxy the MMAs read with: the barrier orders them by itself.
+        if (j + 1 < n_kv && !wait(&kv_full[k_slot], (ik / KV_SLOTS) & 1, 25)) { ok = false; break; }
         for (int t = 0; t < 2; ++t) {
           if (!wait(&p_full[t], j & 1, 24)) { ok = false; break; }
           tc_fence_after_sync();
           issue_pv(t, v_slot, j > 0);
           if (t == 1) commit(&kv_empty[v_slot]);
           if (j + 1 < n_kv) {
-            if (t == 0) {
-              if (!wait(&kv_full[k_slot], (ik / KV_SLOTS) & 1, 25)) { ok = false; break; }
-              tc_fence_after_sync();
-            }
             issue_qk(t, k_slot);
             commit(&s_full[t]);
             if (t == 1) commit(&kv_empty[k_slot]);
