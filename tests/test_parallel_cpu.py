@@ -140,3 +140,16 @@ def test_peer_exchange_layout_places_every_element_once(B, P):
         off = lay["out_offset"] // 4
         out = arenas[r][off:off + B * L_loc * H * D].view(lay["out_shape"])
         torch.testing.assert_close(out, want[:, r * L_loc:(r + 1) * L_loc], atol=1e-5, rtol=1e-5)
+
+
+def test_key_split_estimate_picks_only_part_filled_last_waves():
+    """The attention launch is cut along the keys only where that pays: three local heads at
+    16896 tokens (eight-way sequence parallelism: 198 CTAs on 148 SMs) yes; 6, 12 or 24 heads, the
+    benchmark's single-GPU shape and short sequences no."""
+    from triton_kernels_b200.kernels.attention import key_splits_for
+
+    assert key_splits_for(1, 3, 16896, 16896, 128, 148) == 2
+    assert [key_splits_for(1, h, 16896, 16896, 128, 148) for h in (6, 12, 24)] == [1, 1, 1]
+    assert key_splits_for(1, 24, 4608, 4608, 128, 148) == 1
+    assert key_splits_for(2, 4, 512, 512, 128, 148) == 1  # fewer than eight key tiles: never
+    assert key_splits_for(1, 2, 20480, 20480, 128, 148) == 2
