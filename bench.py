@@ -638,7 +638,8 @@ def run_dit(steps: int, warmup: int, impl: str = "b200"):
 # ranks and an all-to-all on heads around attention.  Strong scaling: the total work is fixed.
 # --------------------------------------------------------------------------------------
 def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: int, exchange: str,
-                    single_rank_baseline: bool = False, scatter_from_projection: bool = False) -> dict:
+                    single_rank_baseline: bool = False, scatter_from_projection: bool = False,
+                    no_graph: bool = False) -> dict:
     """One double-stream block over 16384 image + 512 text tokens with the tokens sharded over the
     ranks of the default process group (which the caller has initialised when world > 1).  With
     `single_rank_baseline` every rank first times the unsharded block on its own GPU, so that the
@@ -695,15 +696,27 @@ def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: 
             sp = block.sequence_parallel = SequenceParallel(exchange=exchange, scatter_from_projection=scatter_from_projection)
             txt_l, img_l, pe_l = shard_joint_sequence(txt, img, pe, rank, world)
             del img, txt
+            calls0 = _lib.kernel_calls
+            block(img_l, txt_l, vec, pe_l)
+            launches = _lib.kernel_calls - calls0
+            step = lambda: block(img_l, txt_l, vec, pe_l)
+            launch = "eager"
+            if exchange == "peer" and not no_graph:
+                # The peer exchange is kernels only (its barriers keep their epochs in the arena), so
+                # the sharded step replays from a CUDA graph like the single-GPU step does; every
+                # rank replays the same number of times.
+                from triton_kernels_b200.flux import GraphedForward
+
+                graphed = GraphedForward(lambda i, t, v: block(i, t, v, pe_l), (img_l, txt_l, vec))
+                step = graphed.graph.replay  # the captured inputs already hold this rank's shard
+                launch = "cuda graph replay"
             sampler = ClockSampler(local_rank)
             sampler.start()
-            calls0 = _lib.kernel_calls
-            ms = timed(lambda: block(img_l, txt_l, vec, pe_l))
-            launches = (_lib.kernel_calls - calls0) // (steps + warmup)
+            ms = timed(step)
             clocks = sampler.stop()
             sp.check()
         else:
-            ms, launches, clocks = single_ms, None, None
+            ms, launches, clocks, launch = single_ms, None, None, "eager"
     tokens = li + lt
     flop = 2 * tokens * C * (3 * C + C + 2 * int(C * MLP_RATIO)) + 4 * H * tokens * tokens * (C // H)
     rec = {
@@ -713,7 +726,7 @@ def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: 
         "exchange": (("stores into peer memory from the producing kernels"
                       + (" (q|k|v from the projection's epilogue)" if scatter_from_projection else ""))
                      if exchange == "peer" else "NCCL all-to-all") if world > 1 else None,
-        "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "steps": steps, "warmup": warmup, "launch": launch,
         "block_tflop": flop / 1e12, "tflops_per_gpu": flop / (ms * 1e-3) / 1e12 / world,
     }
     if single_ms is not None:
@@ -767,7 +780,7 @@ def run_ulysses(args, rank: int, local_rank: int, world: int):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     rec = ulysses_measure(rank, local_rank, world, args.steps, args.warmup, args.exchange, single_rank_baseline=True,
-                          scatter_from_projection=args.sp_scatter_from_projection)
+                          scatter_from_projection=args.sp_scatter_from_projection, no_graph=args.no_graph)
     if rank == 0:
         print(json.dumps({
             "metric": "flux_double_block_fwd_tokens_per_s", "value": rec["tokens_per_s"], "unit": UNIT,
@@ -1249,7 +1262,8 @@ def main():
             # step time sits beside them
             def ulysses_record():
                 recs = {ex: ulysses_measure(rank, local_rank, world, min(args.steps, 20), args.warmup, ex,
-                                            single_rank_baseline=(ex == "peer")) for ex in ("peer", "nccl")}
+                                            single_rank_baseline=(ex == "peer"), no_graph=args.no_graph)
+                        for ex in ("peer", "nccl")}
                 single = recs["peer"]["single_gpu_ms_per_step"]
                 for r in recs.values():
                     r["single_gpu_ms_per_step"] = single
