@@ -808,8 +808,7 @@ extern "C" int fluxb_linear_grouped(const fluxb_linear_problem* problems, int co
   fluxb::gemm2::Grouped g;
   g.count = 0;
   g.total_tiles = 0;
-  static const int stages_env = [] { const char* s = getenv("FLUXB_GEMM_PAIR_STAGES"); return (s && *s) ? atoi(s) : fluxb::gemm2::STAGES; }();
-  g.pair_stages = stages_env < 2 ? 2 : (stages_env > fluxb::gemm2::STAGES ? fluxb::gemm2::STAGES : stages_env);
+  g.pair_stages = fluxb::gemm2::STAGES;
   for (int i = 0; i < count; ++i) {
     if (problems[i].M < 0) return set_error(FLUXB_ERR_BAD_ARG, "linear: negative M");
     if (problems[i].M == 0 || N == 0) continue;  // nothing to compute for this one
