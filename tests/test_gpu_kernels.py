@@ -370,6 +370,31 @@ def test_attention_key_splits(tk, B, H, Lq, Lk, D, splits):
     assert key_splits_for(1, 24, 4608, 4608, 128, 148) == 1
 
 
+def test_empty_inputs_are_no_ops(tk):
+    """Zero tokens: every operator returns an empty tensor of the right shape and launches
+    nothing that could fault (the reference's launchers would start a grid of zero programs)."""
+    from triton_kernels_b200 import ops
+
+    dev = "cuda"
+    w = torch.randn(256, 128, device=dev).to(BF)
+    b = torch.zeros(256, device=dev, dtype=BF)
+    assert tk.linear(torch.empty(2, 0, 128, device=dev, dtype=BF), w, b).shape == (2, 0, 256)
+    assert tk.linear(torch.empty(0, 128, device=dev, dtype=BF), w, None, activation="GELU").shape == (0, 256)
+    q = torch.empty(1, 2, 0, 128, device=dev, dtype=BF)
+    assert tk.scaled_dot_product_attention(q, q, q).shape == (1, 2, 0, 128)
+    x = torch.empty(2, 0, 256, device=dev)
+    sc = torch.zeros(2, 1, 256, device=dev)
+    assert tk.layer_norm_modulation(x, sc, sc).shape == (2, 0, 256)
+    assert tk.rms_norm(torch.empty(1, 3, 0, 128, device=dev), torch.ones(128, device=dev)).shape == (1, 3, 0, 128)
+    oq, ok = tk.apply_rope(q, q, torch.empty(1, 1, 0, 64, 2, 2, device=dev))
+    assert oq.shape == ok.shape == (1, 2, 0, 128)
+    assert ops.silu(torch.empty(0, device=dev)).shape == (0,)
+    torch.cuda.synchronize()
+    from triton_kernels_b200 import _lib
+
+    assert _lib.device_status() == (0, 0)
+
+
 def test_device_status_is_clean(tk):
     from triton_kernels_b200 import _lib
 

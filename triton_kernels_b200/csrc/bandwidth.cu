@@ -1029,9 +1029,10 @@ extern "C" int fluxb_layer_norm_modulation(const void* x, const void* scale, con
                                            fluxb_stream_t stream) {
   if (dtype != FLUXB_F32 && dtype != FLUXB_BF16)
     return set_error(FLUXB_ERR_UNSUPPORTED, "layer_norm_modulation: dtype %d", dtype);
-  if (rows < 0 || cols <= 0 || rows_per_batch <= 0)
+  if (rows < 0 || cols <= 0 || rows_per_batch < 0)
     return set_error(FLUXB_ERR_BAD_ARG, "layer_norm_modulation: bad sizes");
-  if (rows == 0) return FLUXB_OK;
+  if (rows == 0) return FLUXB_OK;  // zero tokens (rows_per_batch is 0 then, too)
+  if (rows_per_batch == 0) return set_error(FLUXB_ERR_BAD_ARG, "layer_norm_modulation: rows_per_batch is 0");
   if (!x || !scale || !shift || !y)
     return set_error(FLUXB_ERR_BAD_ARG, "layer_norm_modulation: null pointer");
   const int vn = vec_elems(dtype);
