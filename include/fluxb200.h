@@ -120,7 +120,9 @@ int fluxb_attention(const void* q, const void* k, const void* v, void* o, int64_
  * `_layer_norm_modulation_fwd` :8-44) and triton_kernels/ops/modulation.py:5-27.
  *   x: rows x cols, row stride x_ld; y: row stride y_ld; batch index = row / rows_per_batch;
  *   scale/shift: cols contiguous, batch stride mod_stride (chunk views of the packed
- *   modulation tensor are passed without copying).  Statistics in fp32, two-pass.
+ *   modulation tensor are passed without copying).  Statistics in fp32: one pass over rows of
+ *   2-24 KB (mean and E[x^2] together; fp32 rows shifted by their first element), mean then
+ *   centred variance otherwise.
  */
 int fluxb_layer_norm_modulation(const void* x, const void* scale, const void* shift, void* y,
                                 int64_t rows, int64_t cols, int64_t rows_per_batch, int64_t x_ld,

@@ -209,11 +209,22 @@ ln_mod_generic_kernel(const T* __restrict__ x, const T* __restrict__ scale,
 }
 
 // ----------------------------------------------------------------------------------------
-// Wide rows (2 KB - 24 KB): the row is fetched by ONE bulk asynchronous copy into shared memory
-// and the three passes read it from there.  A row in flight costs no registers, so every row of
-// a [4608, 3072] problem is resident at once (4 blocks of 8 rows per SM = one wave): all loads
-// are issued in the first microsecond and rows are written back as they complete, instead of
-// two waves of register-resident rows.
+// Wide rows (2 KB - 24 KB): the row is fetched by ONE bulk asynchronous copy into shared memory,
+// one warp per row.  A row in flight costs no registers, so every row of a [4608, 3072] problem
+// is resident at once (2 blocks of 16 rows per SM = one wave): all loads are issued in the first
+// microsecond and rows are written back as they complete.
+//
+// Once a row has landed the warp's cost is shared-memory traffic (32 rows per SM land within a
+// few microseconds of each other and share one 128 B/clock pipe), so the kernel touches the row
+// as few times as it can: ONE pass for the statistics, one pass that reads the row again, applies
+// the modulation and writes the result over it, and a bulk copy out.  With kStagedMod the
+// per-column vectors (scale and shift, or the RMSNorm weight) are fetched once per block into
+// shared memory instead of once per row through L1 (12 KB per 6 KB row otherwise).
+//
+// The LayerNorm statistics are the shifted one-pass form: with p = the row's first element,
+// mean = p + E[x - p] and var = E[(x - p)^2] - E[x - p]^2, accumulated in fp32.  Shifting by an
+// element of the row keeps the subtraction benign when |mean| >> std (the plain
+// E[x^2] - mean^2 form is not).
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile(
@@ -223,7 +234,7 @@ __device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gsrc, 
       : "memory");
 }
 
-// Waits (bounded) for this warp's row.  If the copy never lands the row stays unwritten, so the
+// Waits (bounded) for a staged copy.  If the copy never lands the row stays unwritten, so the
 // give-up is recorded in the device status word like every other bounded wait (site 71).
 __device__ __forceinline__ bool wait_row(uint64_t* bar, DeviceStatus* status) {
   for (uint32_t spin = 0; spin < (1u << 24); ++spin)
@@ -232,77 +243,124 @@ __device__ __forceinline__ bool wait_row(uint64_t* bar, DeviceStatus* status) {
   return false;
 }
 
-template <typename T, bool kLayerNorm>
-__global__ void __launch_bounds__(256, 4)
+constexpr int kBulkHeaderBytes = 256;  // mbarriers: one per warp (up to 16) + one for the vectors
+
+template <typename T, bool kLayerNorm, bool kStagedMod, int kVPL>
+__global__ void __launch_bounds__(512, 2)
 norm_rows_bulk_kernel(const T* __restrict__ x, const T* __restrict__ scale, const T* __restrict__ shift,
                       T* __restrict__ y, float* __restrict__ rstd_out, int64_t rows, int cols,
                       int64_t rows_per_batch, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps,
                       DeviceStatus* status) {
   constexpr int VN = Vec<T>::N;
+  constexpr int kModVecs = kLayerNorm ? 2 : 1;
   extern __shared__ __align__(128) uint8_t bulk_smem[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
   const uint32_t row_bytes = (uint32_t)cols * sizeof(T);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem);  // [8]
-  T* srow = reinterpret_cast<T*>(bulk_smem + 128 + (size_t)warp * row_bytes);
-  const int64_t row = (int64_t)blockIdx.x * 8 + warp;
-  if (row >= rows) return;  // whole warp leaves together; warps never synchronise with each other
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem);  // [warps + 1]
+  T* smod = reinterpret_cast<T*>(bulk_smem + kBulkHeaderBytes);
+  T* srow = reinterpret_cast<T*>(bulk_smem + kBulkHeaderBytes + (kStagedMod ? kModVecs * (size_t)row_bytes : 0) +
+                                 (size_t)warp * row_bytes);
+  const int64_t row = (int64_t)blockIdx.x * warps + warp;
+  // All rows of a block belong to one batch element when kStagedMod (the launcher checks).
+  const int64_t batch = kLayerNorm ? ((int64_t)blockIdx.x * warps) / rows_per_batch : 0;
+  // The per-column vectors are requested BEFORE any row of the block: requests are served roughly
+  // in order, and a vector request queued behind thousands of row requests would land last and
+  // hold every row's second pass until then.
   if (lane == 0) {
     mbar_init(&bars[warp], 1);
+    if (kStagedMod && warp == 0) mbar_init(&bars[warps], 1);
     mbar_fence_init();
     fence_proxy_async_smem();
+    if (kStagedMod && warp == 0) {
+      mbar_expect_tx(&bars[warps], kModVecs * row_bytes);
+      bulk_load_row(smod, scale + batch * mod_stride, row_bytes, &bars[warps]);
+      if (kLayerNorm) bulk_load_row(smod + cols, shift + batch * mod_stride, row_bytes, &bars[warps]);
+    }
+  }
+  if (kStagedMod) __syncthreads();  // the vectors' barrier is initialised before anyone polls it
+  if (lane == 0 && row < rows) {
     mbar_expect_tx(&bars[warp], row_bytes);
     bulk_load_row(srow, x + xaddr.offset(row), row_bytes, &bars[warp]);
   }
   __syncwarp();
+  if (row >= rows) return;  // whole warp leaves together; the warps do not meet again
   if (!wait_row(&bars[warp], status)) return;
 
-  const int nvec = cols / VN;
-  float mean = 0.f;
+  // kVPL > 0: the row is exactly kVPL vectors per lane and the loops unroll completely.
+  const int nvec = kVPL > 0 ? kVPL * 32 : cols / VN;
+  float mean = 0.f, rstd;
   if (kLayerNorm) {
-    float s = 0.f;
+    // 16-bit rows need no shift: their own quantisation (2^-9 of |x|) is 64 times the fp32
+    // cancellation error of the unshifted form at any mean/std ratio.
+    float pivot = 0.f;
+    if (sizeof(T) > 2) {
+      Vec<T> first;
+      first.load(srow);
+      pivot = first.v[0];
+    }
+    float s = 0.f, q = 0.f;
+#pragma unroll(kVPL > 0 ? kVPL : 1)
     for (int i = lane; i < nvec; i += 32) {
       Vec<T> t;
       t.load(srow + i * VN);
 #pragma unroll
-      for (int j = 0; j < VN; ++j) s += t.v[j];
+      for (int j = 0; j < VN; ++j) {
+        const float d = sizeof(T) > 2 ? t.v[j] - pivot : t.v[j];
+        s += d;
+        q = fmaf(d, d, q);
+      }
     }
-    mean = warp_sum(s) / cols;
-  }
-  float q = 0.f;
-  for (int i = lane; i < nvec; i += 32) {
-    Vec<T> t;
-    t.load(srow + i * VN);
+    const float ds = warp_sum(s) / cols;
+    mean = pivot + ds;
+    rstd = rsqrtf(fmaxf(warp_sum(q) / cols - ds * ds, 0.f) + eps);
+  } else {
+    float q = 0.f;
+#pragma unroll(kVPL > 0 ? kVPL : 1)
+    for (int i = lane; i < nvec; i += 32) {
+      Vec<T> t;
+      t.load(srow + i * VN);
 #pragma unroll
-    for (int j = 0; j < VN; ++j) {
-      const float d = t.v[j] - mean;
-      q += d * d;
+      for (int j = 0; j < VN; ++j) q = fmaf(t.v[j], t.v[j], q);
     }
+    rstd = rsqrtf(warp_sum(q) / cols + eps);
+    if (rstd_out != nullptr && lane == 0) rstd_out[row] = rstd;
   }
-  const float rstd = rsqrtf(warp_sum(q) / cols + eps);
-  if (!kLayerNorm && rstd_out != nullptr && lane == 0) rstd_out[row] = rstd;
   // The result replaces the row in shared memory and leaves as ONE bulk copy, like it came: the
   // lanes issue no global stores and the warp's last act is to wait until the copy engine has
   // read the staged row.
   T* yr = y + row * y_ld;
+  if (kStagedMod) {
+    if (!wait_row(&bars[warps], status)) return;
+  }
   if (kLayerNorm) {
-    const int64_t b = row / rows_per_batch;
-    const T* sc = scale + b * mod_stride;
-    const T* sh = shift + b * mod_stride;
+    const int64_t b = kStagedMod ? 0 : row / rows_per_batch;
+    const T* sc = kStagedMod ? smod : scale + b * mod_stride;
+    const T* sh = kStagedMod ? smod + cols : shift + b * mod_stride;
+    const float neg_mean_rstd = -mean * rstd;  // (x - mean) * rstd as one fused multiply-add
+#pragma unroll(kVPL > 0 ? kVPL : 1)
     for (int i = lane; i < nvec; i += 32) {
       Vec<T> t, a, d;
       t.load(srow + i * VN);
-      a.load_nc(sc + i * VN);
-      d.load_nc(sh + i * VN);
+      if (kStagedMod) {
+        a.load(sc + i * VN);
+        d.load(sh + i * VN);
+      } else {
+        a.load_nc(sc + i * VN);
+        d.load_nc(sh + i * VN);
+      }
 #pragma unroll
-      for (int j = 0; j < VN; ++j) t.v[j] = (t.v[j] - mean) * rstd * (1.0f + a.v[j]) + d.v[j];
+      for (int j = 0; j < VN; ++j) t.v[j] = fmaf(fmaf(t.v[j], rstd, neg_mean_rstd), 1.0f + a.v[j], d.v[j]);
       t.store(srow + i * VN);
     }
   } else {
+#pragma unroll(kVPL > 0 ? kVPL : 1)
     for (int i = lane; i < nvec; i += 32) {
       Vec<T> t, wv;
       t.load(srow + i * VN);
-      wv.load_nc(scale + i * VN);
+      if (kStagedMod) wv.load(smod + i * VN);
+      else wv.load_nc(scale + i * VN);
 #pragma unroll
       for (int j = 0; j < VN; ++j) t.v[j] = t.v[j] * rstd * wv.v[j];
       t.store(srow + i * VN);
@@ -327,18 +385,39 @@ static inline bool bulk_rows_ok(int64_t cols, size_t elt, const RowAddr& a) {
   return (a.s0 * (int64_t)elt) % 16 == 0 && (a.s1 * (int64_t)elt) % 16 == 0 && (a.s2 * (int64_t)elt) % 16 == 0;
 }
 
+template <typename T, bool kLayerNorm, bool kStagedMod>
+static int launch_norm_bulk_as(const T* x, const T* scale, const T* shift, T* y, float* rstd, int64_t rows,
+                               int64_t cols, int64_t rpb, RowAddr xaddr, int64_t y_ld, int64_t mod_stride,
+                               float eps, cudaStream_t st) {
+  const int warps = kStagedMod ? 16 : 8;
+  const size_t smem = kBulkHeaderBytes + ((kStagedMod ? (kLayerNorm ? 2 : 1) : 0) + warps) * (size_t)cols * sizeof(T);
+  // Rows of 12 vectors per lane (3072 bf16 columns, the Flux hidden size) get the unrolled form.
+  constexpr int kUnrolled = 12;
+  auto kern = cols == kUnrolled * 32 * Vec<T>::N ? norm_rows_bulk_kernel<T, kLayerNorm, kStagedMod, kUnrolled>
+                                                 : norm_rows_bulk_kernel<T, kLayerNorm, kStagedMod, 0>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess)
+    return set_error(FLUXB_ERR_CUDA, "row norm: cannot set shared memory size: %s", cudaGetErrorString(e));
+  kern<<<(unsigned)((rows + warps - 1) / warps), warps * 32, smem, st>>>(
+      x, scale, shift, y, rstd, rows, (int)cols, rpb, xaddr, y_ld, mod_stride, eps, device_status_ptr());
+  return FLUXB_OK;
+}
+
+// Rows of up to 6 KB whose blocks of 16 rows each stay inside one batch element, with 16-byte
+// aligned per-column vectors, take the form that stages those vectors in shared memory.
 template <typename T, bool kLayerNorm>
 static int launch_norm_bulk(const T* x, const T* scale, const T* shift, T* y, float* rstd, int64_t rows,
                             int64_t cols, int64_t rpb, RowAddr xaddr, int64_t y_ld, int64_t mod_stride, float eps,
                             cudaStream_t st) {
-  const size_t smem = 128 + 8 * (size_t)cols * sizeof(T);
-  auto kern = norm_rows_bulk_kernel<T, kLayerNorm>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess)
-    return set_error(FLUXB_ERR_CUDA, "row norm: cannot set shared memory size: %s", cudaGetErrorString(e));
-  kern<<<(unsigned)((rows + 7) / 8), 256, smem, st>>>(x, scale, shift, y, rstd, rows, (int)cols, rpb, xaddr, y_ld,
-                                                       mod_stride, eps, device_status_ptr());
-  return FLUXB_OK;
+  const bool aligned = (reinterpret_cast<uintptr_t>(scale) & 15) == 0 &&
+                       (!kLayerNorm || ((reinterpret_cast<uintptr_t>(shift) & 15) == 0 &&
+                                        (mod_stride * (int64_t)sizeof(T)) % 16 == 0));
+  const bool one_batch_per_block = !kLayerNorm || rpb % 16 == 0 || rows <= rpb;
+  if (cols * (int64_t)sizeof(T) <= 6144 && aligned && one_batch_per_block)
+    return launch_norm_bulk_as<T, kLayerNorm, true>(x, scale, shift, y, rstd, rows, cols, rpb, xaddr, y_ld,
+                                                    mod_stride, eps, st);
+  return launch_norm_bulk_as<T, kLayerNorm, false>(x, scale, shift, y, rstd, rows, cols, rpb, xaddr, y_ld,
+                                                   mod_stride, eps, st);
 }
 
 template <typename T>
@@ -417,10 +496,11 @@ rms_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict_
 
 // Narrow rows (one 16-byte vector per lane, e.g. the 128-wide per-head rows of q and k): a
 // group of G lanes walks R rows with all R loads issued before the first reduction, so that a
-// thread has R x 16 bytes in flight instead of 16 (at 1024 threads per SM that is 64 KB per SM,
-// enough to cover HBM latency at full bandwidth).
+// thread has R x 16 bytes in flight instead of 16.  Small blocks at high occupancy (128 threads,
+// 12 blocks per SM: 96 KB in flight per SM) measured fastest: blocks retire and start
+// continuously, so loads and stores of different blocks overlap throughout the launch.
 template <typename T, int G, int R>
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(128, 12)
 rms_narrow_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
                        float* __restrict__ rstd_out, int64_t rows, int cols, RowAddr addr, float eps) {
   constexpr int VN = Vec<T>::N;
@@ -502,8 +582,8 @@ static int launch_rms(const void* x, const void* w, void* y, float* rstd, int64_
   }
 #define FLUXB_RMS_NARROW(G)                                                                    \
   if (vecs == (G)) {                                                                           \
-    const int64_t rpb = (256 / (G)) * 4;                                                       \
-    rms_narrow_rows_kernel<T, G, 4><<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, st>>>(       \
+    const int64_t rpb = (128 / (G)) * 4;                                                       \
+    rms_narrow_rows_kernel<T, G, 4><<<(unsigned)((rows + rpb - 1) / rpb), 128, 0, st>>>(       \
         xp, wp, yp, rstd, rows, (int)cols, addr, eps);                                         \
     return FLUXB_OK;                                                                           \
   }
