@@ -94,7 +94,9 @@ int fluxb_linear_grouped(const fluxb_linear_problem* problems, int count, int64_
  * out[b, n] = sum_k silu(vec[b,k]) * w[n,k] + bias[n]  for small b (<= 8): the adaLN
  * modulation projection.  Replaces `Modulation.forward`, triton_kernels/modules/blocks.py:61-67
  * (F.silu + tk.linear with M = batch) and triton_kernels/ops/silu.py:5-13 as its prologue.
- * apply_silu = 0 gives a plain small-M linear.  bf16 storage, fp32 math.
+ * apply_silu = 0 gives a plain small-M linear.  bf16 storage, fp32 accumulation.  For K a
+ * multiple of 1536 silu(vec) is rounded to bf16 before the products (as the reference's bf16
+ * SiLU output is) and the products run on the tensor pipe; other K keep silu(vec) in fp32.
  */
 int fluxb_modulation_gemv(const void* vec, const void* w, const void* bias, void* out, int64_t B,
                           int64_t N, int64_t K, int apply_silu, fluxb_stream_t stream);

@@ -195,7 +195,8 @@ def test_modulation_ops_and_silu(tk, dtype):
     torch.testing.assert_close(ops.silu(v.cuda()).float().cpu(), O.silu(v.float()), **tol)
 
 
-@pytest.mark.parametrize("B,N,K", [(1, 18432, 3072), (2, 9216, 3072), (5, 1000, 256), (8, 64, 3072)])
+@pytest.mark.parametrize("B,N,K", [(1, 18432, 3072), (2, 9216, 3072), (5, 1000, 256), (8, 64, 3072),
+                                   (3, 500, 1536), (1, 301, 4608)])  # one and three chunks per row, ragged N
 def test_modulation_projection(tk, B, N, K):
     from triton_kernels_b200 import ops
 

@@ -933,6 +933,122 @@ silu_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n) {
 }
 
 // ----------------------------------------------------------------------------------------
+// Modulation projection, rows of whole 1536-element chunks (the Flux hidden size is two).
+//
+// The kernel is a 113 MB weight stream (double-stream block) that has to run at HBM speed, so the
+// per-byte work of a lane is kept to almost nothing:
+//  * act(vec) is staged in shared memory as bf16 (the reference's SiLU output is bf16 too) and the
+//    products run on the tensor pipe.  A lane's 16-byte weight load is used AS an mma A fragment
+//    (registers a0..a3 = the four words): word 0/2 sit in fragment row g = lane/4, word 1/3 in row
+//    g+8.  The B fragment of the same lane (column g) is given the activations at the same k
+//    positions as its own weight words, so the diagonal D[g][g] of mma #1 (B from words 0,2) and
+//    D[g+8][g] of mma #2 (B from words 1,3) accumulate exactly that lane group's products.  The row
+//    result is the sum of the diagonals over the warp.  Two mma per 16-byte load replace eight
+//    unpacks, eight multiply-adds and 32 bytes of shared-memory reads.
+//  * vec is requested before any weight (a request behind the weight stream comes back last), and
+//    half-row chunks of six loads per lane are double-buffered across row boundaries.
+//  * the grid is balanced: every warp gets the same number of rows when N allows it.
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+
+template <int BT>
+__global__ void __launch_bounds__(512, 2)
+mod_gemv_mma_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __restrict__ w,
+                    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
+                    int K, int64_t b0, int apply_silu) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(gemv_smem);  // act(vec) [BT][K]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps = blockDim.x >> 5;
+  const int cpr = K / 1536;
+  // rows are counted in 32 bits (the launcher checks N): 64-bit row arithmetic costs registers
+  const int n_rows = (int)N;
+  const int stride = gridDim.x * warps;
+  int row = blockIdx.x * warps + warp;
+  // vec first
+  const int nv = BT * K / 8;
+  constexpr int kVecRegs = 1;  // one 16-byte piece per thread covers BT x K up to 4096 elements
+  uint4 myvec[kVecRegs];
+#pragma unroll
+  for (int r = 0; r < kVecRegs; ++r) {
+    const int i = threadIdx.x + r * 512;
+    if (i < nv) myvec[r] = ld_nc_u4(vec + b0 * K + (int64_t)i * 8);
+  }
+  uint4 cur[6], nxt[6];
+  if (row < n_rows) {
+#pragma unroll
+    for (int u = 0; u < 6; ++u) cur[u] = ld_nc_u4(w + (int64_t)row * K + lane * 8 + u * 256);
+  }
+  auto stage = [&](const uint4& raw, int i) {
+    Vec<__nv_bfloat16> t;
+    t.unpack(raw);
+    if (apply_silu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t.v[j] = silu_f(t.v[j]);
+    }
+    t.store(sa + (int64_t)i * 8);
+  };
+#pragma unroll
+  for (int r = 0; r < kVecRegs; ++r) {
+    const int i = threadIdx.x + r * 512;
+    if (i < nv) stage(myvec[r], i);
+  }
+  for (int i = threadIdx.x + kVecRegs * 512; i < nv; i += 512) stage(ld_nc_u4(vec + b0 * K + (int64_t)i * 8), i);
+  __syncthreads();
+
+  float c1[BT][4], c2[BT][4];
+#pragma unroll
+  for (int bb = 0; bb < BT; ++bb)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) c1[bb][j] = c2[bb][j] = 0.f;
+  const int g = lane >> 2;
+  const bool on_diagonal = (lane & 3) == (g >> 1);
+  int ch = 0;
+  while (row < n_rows) {
+    const bool last = ch + 1 == cpr;
+    const int nrow = last ? row + stride : row;
+    const int nch = last ? 0 : ch + 1;
+    if (nrow < n_rows) {
+#pragma unroll
+      for (int u = 0; u < 6; ++u) nxt[u] = ld_nc_u4(w + (int64_t)nrow * K + nch * 1536 + lane * 8 + u * 256);
+    }
+    const __nv_bfloat16* sac = sa + ch * 1536 + lane * 8;
+#pragma unroll
+    for (int u = 0; u < 6; ++u) {
+#pragma unroll
+      for (int bb = 0; bb < BT; ++bb) {
+        const uint4 a = *reinterpret_cast<const uint4*>(sac + bb * K + u * 256);
+        mma_bf16_16x8x16(c1[bb], cur[u], a.x, a.z);
+        mma_bf16_16x8x16(c2[bb], cur[u], a.y, a.w);
+      }
+    }
+    if (last) {
+#pragma unroll
+      for (int bb = 0; bb < BT; ++bb) {
+        const float mine = on_diagonal ? ((g & 1) ? c1[bb][1] + c2[bb][3] : c1[bb][0] + c2[bb][2]) : 0.f;
+        const float sum = warp_sum(mine);
+        if (lane == 0) {
+          const float bv = bias != nullptr ? __bfloat162float(bias[row]) : 0.f;
+          out[(b0 + bb) * N + row] = __float2bfloat16_rn(sum + bv);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c1[bb][j] = c2[bb][j] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 6; ++u) cur[u] = nxt[u];
+    row = nrow;
+    ch = nch;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // Modulation projection: out[b,n] = sum_k act(vec[b,k]) w[n,k] + bias[n], bf16 weights read
 // exactly once per batch tile of BT rows.  One warp per output column n; act(vec) staged in
 // shared memory as fp32.
@@ -943,18 +1059,6 @@ mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __re
                 const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
                 int K, int64_t b0, int apply_silu) {
   extern __shared__ float sv[];  // [BT][K]
-  // first chunk of this warp's first row: requested before act(vec) is staged, so that the
-  // weight stream starts with the kernel and not after the block's first barrier
-  const bool chunked = K % 1536 == 0;
-  uint4 cur[6];
-  if (chunked) {
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row < N) {
-#pragma unroll
-      for (int u = 0; u < 6; ++u)
-        cur[u] = __ldg(reinterpret_cast<const uint4*>(w + row * K + (threadIdx.x & 31) * 8 + u * 256));
-    }
-  }
   for (int i = threadIdx.x; i < BT * K; i += blockDim.x) {
     const int bb = i / K, kk = i % K;
     float t = __bfloat162float(vec[(b0 + bb) * K + kk]);
@@ -965,61 +1069,7 @@ mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __re
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps = blockDim.x >> 5;
-  // A few persistent blocks per SM; every warp walks output columns with a grid stride, four
-  // 16-byte weight loads in flight per lane.
-  if (chunked) {
-    // Rows that are whole multiples of 1536 elements (the Flux hidden size is two) are streamed
-    // as half-row chunks of six 16-byte loads per lane, and the loads of chunk i+1 are issued
-    // before chunk i is consumed: a warp always has a chunk in flight, across row boundaries too,
-    // where the form below drains its load queue between two rows.
-    const int cpr = K / 1536;
-    const int64_t stride = (int64_t)gridDim.x * warps;
-    int64_t row = (int64_t)blockIdx.x * warps + warp;
-    int ch = 0;
-    uint4 nxt[6];
-    float acc[BT];
-#pragma unroll
-    for (int bb = 0; bb < BT; ++bb) acc[bb] = 0.f;
-    while (row < N) {
-      const bool last = ch + 1 == cpr;
-      const int64_t nrow = last ? row + stride : row;
-      const int nch = last ? 0 : ch + 1;
-      if (nrow < N) {
-#pragma unroll
-        for (int u = 0; u < 6; ++u)
-          nxt[u] = __ldg(reinterpret_cast<const uint4*>(w + nrow * K + nch * 1536 + lane * 8 + u * 256));
-      }
-      const float* svc = sv + ch * 1536 + lane * 8;
-#pragma unroll
-      for (int u = 0; u < 6; ++u) {
-        Vec<__nv_bfloat16> wv;
-        wv.unpack(cur[u]);
-#pragma unroll
-        for (int bb = 0; bb < BT; ++bb) {
-          const float4 a0 = *reinterpret_cast<const float4*>(svc + bb * K + u * 256);
-          const float4 a1 = *reinterpret_cast<const float4*>(svc + bb * K + u * 256 + 4);
-          acc[bb] += wv.v[0] * a0.x + wv.v[1] * a0.y + wv.v[2] * a0.z + wv.v[3] * a0.w +
-                     wv.v[4] * a1.x + wv.v[5] * a1.y + wv.v[6] * a1.z + wv.v[7] * a1.w;
-        }
-      }
-      if (last) {
-#pragma unroll
-        for (int bb = 0; bb < BT; ++bb) {
-          const float sum = warp_sum(acc[bb]);
-          if (lane == 0) {
-            const float bv = bias != nullptr ? __bfloat162float(bias[row]) : 0.f;
-            out[(b0 + bb) * N + row] = __float2bfloat16_rn(sum + bv);
-          }
-          acc[bb] = 0.f;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 6; ++u) cur[u] = nxt[u];
-      row = nrow;
-      ch = nch;
-    }
-    return;
-  }
+  // A few persistent blocks per SM; every warp walks output columns with a grid stride.
   for (int64_t n = (int64_t)blockIdx.x * warps + warp; n < N; n += (int64_t)gridDim.x * warps) {
     const __nv_bfloat16* wr = w + n * K;
     float acc[BT];
@@ -1444,36 +1494,38 @@ extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void*
   if (K % 8 || !aligned16(w) || !aligned16(vec))
     return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: K must be a multiple of 8 and pointers 16-byte aligned");
   if (K > 12288) return set_error(FLUXB_ERR_UNSUPPORTED, "modulation_gemv: K %lld > 12288", (long long)K);
+  if (N > (int64_t)1 << 30) return set_error(FLUXB_ERR_UNSUPPORTED, "modulation_gemv: N %lld > 2^30", (long long)N);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(vec);
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
   const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+  // Two 512-thread blocks fit on an SM.  The grid is the number of 16-row groups divided evenly
+  // over the fewest rounds that fit that many resident blocks: every warp then walks the same
+  // number of rows (18432 rows: 288 blocks of 4 rounds, not 296 of 3.9).
   const int64_t want = (N + 15) / 16;
-  // Two 512-thread blocks fit on an SM: a grid of exactly that many stages act(vec) once per
-  // resident block and then only streams weights (measured 35 us against 37-38 us with twice as
-  // many blocks on the 113 MB double-block projection).
   const int64_t cap = (int64_t)sm_count() * 2;
-  const unsigned grid = (unsigned)(want < cap ? want : cap);
+  const int64_t rounds = (want + cap - 1) / cap;
+  const unsigned grid = (unsigned)((want + rounds - 1) / rounds);
+  const bool chunked = K % 1536 == 0;
   int64_t b0 = 0;
+#define FLUXB_GEMV_LAUNCH(BT)                                                                          \
+  {                                                                                                    \
+    auto kern = chunked ? mod_gemv_mma_kernel<((BT) > 2 ? 2 : (BT))> : mod_gemv_kernel<BT>;                               \
+    const size_t smem = (size_t)(BT) * K * (chunked ? sizeof(__nv_bfloat16) : sizeof(float));          \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e != cudaSuccess)                                                                              \
+      return set_error(FLUXB_ERR_CUDA, "modulation_gemv: cannot set shared memory size: %s",           \
+                       cudaGetErrorString(e));                                                         \
+    kern<<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);                          \
+    b0 += (BT);                                                                                        \
+  }
   while (b0 < B) {
     const int64_t left = B - b0;
-    if (left >= 4) {
-      const size_t smem = (size_t)4 * K * sizeof(float);
-      cudaFuncSetAttribute(mod_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      mod_gemv_kernel<4><<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
-      b0 += 4;
-    } else if (left >= 2) {
-      const size_t smem = (size_t)2 * K * sizeof(float);
-      cudaFuncSetAttribute(mod_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      mod_gemv_kernel<2><<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
-      b0 += 2;
-    } else {
-      const size_t smem = (size_t)K * sizeof(float);
-      cudaFuncSetAttribute(mod_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      mod_gemv_kernel<1><<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);
-      b0 += 1;
-    }
+    if (left >= 4 && !chunked) FLUXB_GEMV_LAUNCH(4)  // the mma form keeps 8 accumulators per batch row
+    else if (left >= 2) FLUXB_GEMV_LAUNCH(2)
+    else FLUXB_GEMV_LAUNCH(1)
   }
+#undef FLUXB_GEMV_LAUNCH
   return launch_status("modulation_gemv");
 }
