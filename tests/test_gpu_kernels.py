@@ -55,6 +55,22 @@ def test_layer_norm_modulation_bf16(tk, B, L, N, eps):
     close_bf16(y, O.layer_norm_modulation(x.float(), sc.float(), sh.float(), eps=eps))
 
 
+@pytest.mark.parametrize("mean", [50.0, -200.0])
+def test_layer_norm_modulation_rows_far_from_zero(tk, mean):
+    """The wide-row kernel takes its statistics in one pass (sum and sum of squares).  Rows whose
+    mean is many standard deviations from zero are where that form cancels: fp32 rows are shifted
+    by their first element, 16-bit rows rely on their own quantisation being the larger error."""
+    g = gen(21)
+    B, L, N = 1, 64, 3072
+    sc, sh = 0.1 * torch.randn(B, 1, N, generator=g), 0.1 * torch.randn(B, 1, N, generator=g)
+    x = torch.randn(B, L, N, generator=g) + mean
+    y = tk.layer_norm_modulation(x.cuda(), sc.cuda(), sh.cuda(), eps=1e-6)
+    torch.testing.assert_close(y.cpu(), O.layer_norm_modulation(x, sc, sh, eps=1e-6), atol=2e-4, rtol=2e-4)
+    xb, scb, shb = x.to(BF), sc.to(BF), sh.to(BF)
+    yb = tk.layer_norm_modulation(xb.cuda(), scb.cuda(), shb.cuda(), eps=1e-6)
+    close_bf16(yb, O.layer_norm_modulation(xb.float(), scb.float(), shb.float(), eps=1e-6))
+
+
 def test_layer_norm_modulation_reads_packed_chunks_in_place(tk):
     """scale/shift given as chunk views of a packed [B, 6C] tensor (no copies needed)."""
     g = gen(3)

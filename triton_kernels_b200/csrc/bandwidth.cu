@@ -3,10 +3,14 @@
 // concat), modulation scale/shift and gate/residual, SiLU, and the small-batch modulation
 // projection (a GEMV over bf16 weights).
 //
-// Common shape of every kernel: 16-byte vector loads/stores, one row (or row segment) held in
-// registers, fp32 statistics with a centred second pass, reductions by warp shuffles only.
-// Algorithmic traffic is "every input once, every output once"; nothing is staged through
-// global scratch.
+// Common shape of every kernel: 16-byte vector loads/stores, a row (or row segment) held in
+// registers or, for rows of 2-24 KB, staged in shared memory by a bulk copy; fp32 statistics
+// (one pass over staged rows, mean then centred variance over register-held rows), reductions
+// by warp shuffles only.  Algorithmic traffic is "every input once, every output once"; nothing
+// is staged through global scratch.  The 57-113 MB problems of the block are short enough
+// (10-20 us) that issue slots, shared-memory traffic and the order in which requests are made
+// decide their speed as much as the byte count does; the comments at each kernel say what was
+// measured.
 #include <stdarg.h>
 #include <stdio.h>
 

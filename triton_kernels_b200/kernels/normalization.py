@@ -27,7 +27,8 @@ def layer_norm_modulation_into(x2d, scale2d, shift2d, y2d, rows_per_batch: int, 
 def layer_norm_modulation(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
     """LayerNorm(x) without affine, then `* (1 + weight) + bias` with weight/bias of shape
     [B, 1, C] broadcast over the sequence (reference :47-77; its default eps 1e-5 is kept).
-    Statistics are fp32 and two-pass whatever the storage dtype."""
+    Statistics are fp32 whatever the storage dtype (rows of 2-24 KB: sum and sum of squares in
+    one pass, fp32 rows shifted by their first element; other widths: mean, then centred variance)."""
     assert x.shape[0] == weight.shape[0] == bias.shape[0]
     assert x.shape[-1] == weight.shape[-1] == bias.shape[-1]
     _lib.require_cuda(x, weight, bias)
