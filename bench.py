@@ -677,16 +677,36 @@ def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: 
         return float(t.item())
 
     def timed(fn):
-        for _ in range(warmup):
+        """Milliseconds per step, max over ranks.  The one-GPU step is four to eight times longer
+        than a sharded one, so equal step counts would time the former at the power cap and the
+        latter in the first, faster milliseconds after it: every form is therefore warmed up for
+        at least 0.25 s and timed over at least 0.25 s (never fewer than `warmup` / `steps` steps;
+        the counts come from an all-reduced estimate, so all ranks run the same number)."""
+        for _ in range(3):
             fn()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for _ in range(3):
             fn()
         e1.record()
         barrier()
-        return max_over_ranks(e0.elapsed_time(e1)) / steps
+        est_ms = max(max_over_ranks(e0.elapsed_time(e1)) / 3, 1e-3)
+        n_warm = max(warmup, int(250.0 / est_ms) + 1)
+        n_timed = max(steps, int(250.0 / est_ms) + 1)
+        for _ in range(n_warm):
+            fn()
+        barrier()
+        e0.record()
+        for _ in range(n_timed):
+            fn()
+        e1.record()
+        barrier()
+        counts["steps"] = n_timed
+        counts["warmup"] = n_warm + 6
+        return max_over_ranks(e0.elapsed_time(e1)) / n_timed
+
+    counts: dict = {}
 
     single_ms = None
     with torch.no_grad():
@@ -726,7 +746,10 @@ def ulysses_measure(rank: int, local_rank: int, world: int, steps: int, warmup: 
         "exchange": (("stores into peer memory from the producing kernels"
                       + (" (q|k|v from the projection's epilogue)" if scatter_from_projection else ""))
                      if exchange == "peer" else "NCCL all-to-all") if world > 1 else None,
-        "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "steps": steps, "warmup": warmup, "launch": launch,
+        "ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3), "steps": counts.get("steps", steps),
+        "warmup": counts.get("warmup", warmup), "launch": launch,
+        "timing": "each form warmed up for at least 0.25 s and timed over at least 0.25 s, so that the one-GPU step and the "
+                  "shorter sharded steps are all measured in the same (power-capped) regime",
         "block_tflop": flop / 1e12, "tflops_per_gpu": flop / (ms * 1e-3) / 1e12 / world,
     }
     if single_ms is not None:

@@ -96,8 +96,10 @@ def _rank_main(rank: int, world: int, port: int, q_out):
             txt2_l, img2_l, pe2_l = shard_joint_sequence(txt2, img2, pe2, rank, world)
             ri = slice(rank * (gh2 * gw2 // world), (rank + 1) * (gh2 * gw2 // world))
             rt = slice(rank * (Lt2 // world), (rank + 1) * (Lt2 // world))
-            for exchange in ("peer", "nccl"):
-                sp = SequenceParallel(exchange=exchange)
+            # peer exchange with the image tokens projected and scattered in two halves (the default
+            # for 512 local image tokens and more) and in one piece
+            for exchange, pipelined in (("peer", True), ("peer", False), ("nccl", False)):
+                sp = SequenceParallel(exchange=exchange, pipeline_exchange=pipelined)
                 blk2.sequence_parallel = sp
                 for _ in range(2):
                     got_i2, got_t2 = blk2(img2_l, txt2_l, vec2, pe2_l)

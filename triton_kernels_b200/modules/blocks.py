@@ -384,6 +384,31 @@ class DoubleStreamBlock(nn.Module):
                 dict(x=h, w=a.qkv.weight, b=a.qkv.bias, q_scale=a.norm.query_norm.scale, k_scale=a.norm.key_norm.scale)
                 for h, a in zip(h1, attns)], pe, None, eps=1e-6, scatter=_scatter_target(pb, H, D))
             attn = _peer_attention(pb, Lt + Li, D**-0.5, None)
+        elif (sp is not None and sp.world > 1 and sp.exchange == "peer" and sp.pipeline_exchange and B == 1
+              and Li >= 512):
+            # sequence parallel, peer exchange: project and scatter the image tokens in two halves so
+            # that the first half's stores into the peers' arenas (NVLink-bound, few issue slots)
+            # run beside the second half's projection instead of after it
+            pb = sp.peer_buffers(B, Lt + Li, H, D, dt)
+            half = (Li // 2 + 127) // 128 * 128
+            qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]
+            x_img, y_img = h1[1].view(Li, C), qkvs[1].view(Li, 3 * C)
+            a_t, a_i = attns
+            norms = [(a.norm.query_norm.scale.to(dt), a.norm.key_norm.scale.to(dt)) for a in attns]
+            pe_rows = pe.reshape(-1, D // 2, 2, 2)
+            scat = (pb.P, pb.k_off, pb.v_off, H, D, pb.qkv_strides)
+            linear_grouped_into([
+                dict(x2d=h1[0].view(Lt, C), w=a_t.qkv.weight, b=a_t.qkv.bias, y=qkvs[0].view(Lt, 3 * C)),
+                dict(x2d=x_img[:half], w=a_i.qkv.weight, b=a_i.qkv.bias, y=y_img[:half])])
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                qkv_prepare_scatter([(qkvs[0], *norms[0]), (qkvs[1][:, :half], *norms[1])], pe_rows[: Lt + half],
+                                    pb.q_bases, *scat, eps=1e-6)
+            linear_grouped_into([dict(x2d=x_img[half:], w=a_i.qkv.weight, b=a_i.qkv.bias, y=y_img[half:])])
+            qkv_prepare_scatter([(qkvs[1][:, half:], *norms[1])], pe_rows[Lt + half :],
+                                pb.q_bases_from_row(Lt + half), *scat, eps=1e-6)
+            main.wait_stream(side)
+            attn = _peer_attention(pb, Lt + Li, D**-0.5, None)
         else:
             # both streams' qkv projections in one launch, then the assembly kernel
             qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]

@@ -40,8 +40,13 @@ from torch import Tensor
 class SequenceParallel:
     """Process-group handle plus the two layout-changing exchanges."""
 
-    def __init__(self, group=None, exchange: str = "nccl", scatter_from_projection: bool = False):
-        """`scatter_from_projection` (peer exchange only): let the q|k|v projection's own epilogue
+    def __init__(self, group=None, exchange: str = "nccl", scatter_from_projection: bool = False,
+                 pipeline_exchange: bool = True):
+        """`pipeline_exchange` (peer exchange only): the double-stream block projects and scatters
+        its image tokens in two halves, the first half's stores into the peers' arenas running
+        beside the second half's projection on a second stream.
+
+        `scatter_from_projection` (peer exchange only): let the q|k|v projection's own epilogue
         store every head group into its owner's arena (fluxb_linear_qkv_grouped_scatter) instead
         of running the assembly kernel after the projection.  Off by default: with half of the
         stores going over NVLink the GEMM's epilogue warps stall on them, and on two B200s the
@@ -53,6 +58,7 @@ class SequenceParallel:
         self.world = dist.get_world_size(group)
         self.exchange = exchange
         self.scatter_from_projection = bool(scatter_from_projection) and exchange == "peer"
+        self.pipeline_exchange = bool(pipeline_exchange) and exchange == "peer"
         self._peer: dict = {}
 
     # ---- peer-memory exchange ------------------------------------------------------------
@@ -164,10 +170,24 @@ class _PeerBuffers:
         self.out = self.arena.local_view(lay["out_offset"], lay["out_shape"], dtype)
         self.P, self.Hp, self.L_loc = P, lay["Hp"], L_loc
         self.k_off, self.v_off = lay["k_off"], lay["v_off"]
-        self.q_bases = (ctypes.c_void_p * P)(*[self.arena.address(g, off) for g, off in enumerate(lay["q_offsets"])])
+        self._q_addr = [int(self.arena.address(g, off)) for g, off in enumerate(lay["q_offsets"])]
+        self._elem_size = torch.empty((), dtype=dtype).element_size()
+        self.q_bases = (ctypes.c_void_p * P)(*self._q_addr)
+        self._q_bases_from = {0: self.q_bases}
         self.qkv_strides = lay["qkv_strides"]
         self.o_bases = (ctypes.c_void_p * P)(*[self.arena.address(r, off) for r, off in enumerate(lay["o_offsets"])])
         self.o_strides = lay["o_strides"]
+
+
+    def q_bases_from_row(self, row: int):
+        """The q address table for local tokens starting at `row` (a scatter call that handles the
+        rows [row, ...) of this rank's tokens numbers them from zero)."""
+        if row not in self._q_bases_from:
+            import ctypes
+
+            step = row * self.qkv_strides[2] * self._elem_size
+            self._q_bases_from[row] = (ctypes.c_void_p * self.P)(*[a + step for a in self._q_addr])
+        return self._q_bases_from[row]
 
 
 def shard_joint_sequence(txt: Tensor, img: Tensor, pe: Tensor, rank: int, world: int):
