@@ -43,8 +43,9 @@ class SequenceParallel:
     def __init__(self, group=None, exchange: str = "nccl", scatter_from_projection: bool = False,
                  pipeline_exchange: bool = True):
         """`pipeline_exchange` (peer exchange only): the double-stream block projects and scatters
-        its image tokens in two halves, the first half's stores into the peers' arenas running
-        beside the second half's projection on a second stream.
+        its image tokens in two pieces, the first piece's stores into the peers' arenas running
+        beside the second piece's projection on a second stream (1.81 against 1.83 ms per step
+        on four B200s with every form timed at the power cap).
 
         `scatter_from_projection` (peer exchange only): let the q|k|v projection's own epilogue
         store every head group into its owner's arena (fluxb_linear_qkv_grouped_scatter) instead
