@@ -68,14 +68,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// tanh-form GELU, 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), evaluated in fp32.
-// tanh(u) = 1 - 2 / (1 + exp(2u)) keeps full fp32 accuracy with one exp and one divide.
+__device__ __forceinline__ float exp2f_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// tanh-form GELU, 0.5 x (1 + tanh(u)) with u = sqrt(2/pi) (x + 0.044715 x^3), evaluated in fp32.
+// 0.5 (1 + tanh(u)) = 1 / (1 + exp(-2u)), so the whole function is x times a logistic: one exp2 and
+// one reciprocal on the special-function unit and five multiply-adds, with -2 log2(e) sqrt(2/pi)
+// folded into the polynomial's coefficients.  Accurate in relative terms on both tails (for very
+// negative x the logistic underflows to 0 and the result is -0).
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float c = 0.7978845608028654f;
-  float u = c * (x + 0.044715f * x * x * x);
-  float e = __expf(2.0f * u);
-  float t = 1.0f - __fdividef(2.0f, 1.0f + e);
-  return 0.5f * x * (1.0f + t);
+  const float k1 = -2.0f * 1.4426950408889634f * 0.7978845608028654f;  // -2 log2(e) sqrt(2/pi)
+  const float k2 = k1 * 0.044715f;
+  const float x2 = x * x;
+  const float e = exp2f_approx(x * fmaf(x2, k2, k1));  // exp(-2u)
+  return x * __fdividef(1.0f, 1.0f + e);
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
