@@ -102,6 +102,18 @@ int fluxb_modulation_gemv(const void* vec, const void* w, const void* bias, void
                           int64_t N, int64_t K, int apply_silu, fluxb_stream_t stream);
 
 /*
+ * fluxb_modulation_gemv over a range of output rows: w, bias and out point at the first row of the
+ * range (N rows), out rows of different batch items lie out_stride elements apart (the packed
+ * [B, 6C] modulation tensor is filled in two calls).  light != 0 launches 128-thread blocks, at
+ * most two per SM, which fit beside a tensor-core kernel holding one block per SM: the half of
+ * the projection that is needed only after attention streams its weights during the q|k|v GEMM.
+ * No counterpart in the reference (its Modulation is one `linear` call).
+ */
+int fluxb_modulation_gemv_rows(const void* vec, const void* w, const void* bias, void* out,
+                               int64_t B, int64_t N, int64_t K, int64_t out_stride, int apply_silu,
+                               int light, fluxb_stream_t stream);
+
+/*
  * Non-causal attention softmax(q k^T * sm_scale) v, bf16, head_dim 64 or 128.
  * Replaces triton_kernels/kernels/attention.py:173-221 (`scaled_dot_product_attention`,
  * kernels `_attn_fwd` :69-170 / `_attn_fwd_inner` :10-46).

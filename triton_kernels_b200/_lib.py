@@ -49,6 +49,7 @@ SIGNATURES = {
     "fluxb_linear_qkv_grouped_scatter": (_I, [POINTER(LinearProblem), POINTER(QkvStream), _I, _L, _L, _L, _L, _L,
                                               POINTER(c_void_p), _I, _L, _L, _L, _L, _L, _F, _L, _I, _I, _P]),
     "fluxb_modulation_gemv": (_I, [_P, _P, _P, _P, _L, _L, _L, _I, _P]),
+    "fluxb_modulation_gemv_rows": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _I, _I, _P]),
     "fluxb_attention": (_I, [_P, _P, _P, _P] + [_L] * 5 + [_L] * 12 + [_F, _P]),
     "fluxb_layer_norm_modulation": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _F, _I, _P]),
     "fluxb_rms_norm": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _F, _I, _P]),

@@ -1006,7 +1006,7 @@ template <int BT>
 __global__ void __launch_bounds__(512, 2)
 mod_gemv_mma_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __restrict__ w,
                     const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
-                    int K, int64_t b0, int apply_silu) {
+                    int K, int64_t b0, int apply_silu, int64_t out_stride) {
   extern __shared__ __align__(16) uint8_t gemv_smem[];
   __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(gemv_smem);  // act(vec) [BT][K]
   const int lane = threadIdx.x & 31;
@@ -1019,11 +1019,12 @@ mod_gemv_mma_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* 
   int row = blockIdx.x * warps + warp;
   // vec first
   const int nv = BT * K / 8;
-  constexpr int kVecRegs = 1;  // one 16-byte piece per thread covers BT x K up to 4096 elements
+  constexpr int kVecRegs = 1;  // one 16-byte piece per thread (512 threads cover BT x K up to 4096 elements)
   uint4 myvec[kVecRegs];
+  const int nthr = blockDim.x;
 #pragma unroll
   for (int r = 0; r < kVecRegs; ++r) {
-    const int i = threadIdx.x + r * 512;
+    const int i = threadIdx.x + r * nthr;
     if (i < nv) myvec[r] = ld_nc_u4(vec + b0 * K + (int64_t)i * 8);
   }
   uint4 cur[6], nxt[6];
@@ -1042,10 +1043,10 @@ mod_gemv_mma_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* 
   };
 #pragma unroll
   for (int r = 0; r < kVecRegs; ++r) {
-    const int i = threadIdx.x + r * 512;
+    const int i = threadIdx.x + r * nthr;
     if (i < nv) stage(myvec[r], i);
   }
-  for (int i = threadIdx.x + kVecRegs * 512; i < nv; i += 512) stage(ld_nc_u4(vec + b0 * K + (int64_t)i * 8), i);
+  for (int i = threadIdx.x + kVecRegs * nthr; i < nv; i += nthr) stage(ld_nc_u4(vec + b0 * K + (int64_t)i * 8), i);
   __syncthreads();
 
   float c1[BT][4], c2[BT][4];
@@ -1081,7 +1082,7 @@ mod_gemv_mma_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* 
         const float sum = warp_sum(mine);
         if (lane == 0) {
           const float bv = bias != nullptr ? __bfloat162float(bias[row]) : 0.f;
-          out[(b0 + bb) * N + row] = __float2bfloat16_rn(sum + bv);
+          out[(b0 + bb) * out_stride + row] = __float2bfloat16_rn(sum + bv);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) c1[bb][j] = c2[bb][j] = 0.f;
@@ -1103,7 +1104,7 @@ template <int BT>
 __global__ void __launch_bounds__(512, 2)
 mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __restrict__ w,
                 const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t N,
-                int K, int64_t b0, int apply_silu) {
+                int K, int64_t b0, int apply_silu, int64_t out_stride) {
   extern __shared__ float sv[];  // [BT][K]
   for (int i = threadIdx.x; i < BT * K; i += blockDim.x) {
     const int bb = i / K, kk = i % K;
@@ -1177,7 +1178,7 @@ mod_gemv_kernel(const __nv_bfloat16* __restrict__ vec, const __nv_bfloat16* __re
       const float s = warp_sum(acc[bb]);
       if (lane == 0) {
         const float bv = bias != nullptr ? __bfloat162float(bias[n]) : 0.f;
-        out[(b0 + bb) * N + n] = __float2bfloat16_rn(s + bv);
+        out[(b0 + bb) * out_stride + n] = __float2bfloat16_rn(s + bv);
       }
     }
   }
@@ -1541,10 +1542,13 @@ extern "C" int fluxb_silu(const void* x, void* out, int64_t n, int dtype, fluxb_
   return launch_status("silu");
 }
 
-extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void* bias, void* out,
-                                     int64_t B, int64_t N, int64_t K, int apply_silu,
-                                     fluxb_stream_t stream) {
-  if (B < 0 || N < 0 || K <= 0) return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: bad sizes");
+// `light`: 128-thread blocks, at most two per SM: few enough registers, threads and shared memory
+// to be resident beside a tensor-core kernel that holds one persistent block per SM, so that a
+// projection whose result is needed later streams its weights while that kernel computes.
+static int modulation_gemv_impl(const void* vec, const void* w, const void* bias, void* out, int64_t B,
+                                int64_t N, int64_t K, int64_t out_stride, int apply_silu, bool light,
+                                fluxb_stream_t stream) {
+  if (B < 0 || N < 0 || K <= 0 || out_stride < N) return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: bad sizes");
   if (B == 0 || N == 0) return FLUXB_OK;
   if (!vec || !w || !out) return set_error(FLUXB_ERR_BAD_ARG, "modulation_gemv: null pointer");
   if (K % 8 || !aligned16(w) || !aligned16(vec))
@@ -1556,10 +1560,11 @@ extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void*
   const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
   const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
   __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
-  // Two 512-thread blocks fit on an SM.  The grid is the number of 16-row groups divided evenly
-  // over the fewest rounds that fit that many resident blocks: every warp then walks the same
-  // number of rows (18432 rows: 288 blocks of 4 rounds, not 296 of 3.9).
-  const int64_t want = (N + 15) / 16;
+  // Two blocks fit on an SM.  The grid is the number of row groups (one row per warp) divided
+  // evenly over the fewest rounds that fit that many resident blocks: every warp then walks the
+  // same number of rows (18432 rows, 16 warps per block: 288 blocks of 4 rounds, not 296 of 3.9).
+  const int threads = light ? 128 : 512;
+  const int64_t want = (N + threads / 32 - 1) / (threads / 32);
   const int64_t cap = (int64_t)sm_count() * 2;
   const int64_t rounds = (want + cap - 1) / cap;
   const unsigned grid = (unsigned)((want + rounds - 1) / rounds);
@@ -1567,13 +1572,13 @@ extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void*
   int64_t b0 = 0;
 #define FLUXB_GEMV_LAUNCH(BT)                                                                          \
   {                                                                                                    \
-    auto kern = chunked ? mod_gemv_mma_kernel<((BT) > 2 ? 2 : (BT))> : mod_gemv_kernel<BT>;                               \
+    auto kern = chunked ? mod_gemv_mma_kernel<((BT) > 2 ? 2 : (BT))> : mod_gemv_kernel<BT>;            \
     const size_t smem = (size_t)(BT) * K * (chunked ? sizeof(__nv_bfloat16) : sizeof(float));          \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess)                                                                              \
       return set_error(FLUXB_ERR_CUDA, "modulation_gemv: cannot set shared memory size: %s",           \
                        cudaGetErrorString(e));                                                         \
-    kern<<<grid, 512, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu);                          \
+    kern<<<grid, threads, smem, st>>>(vp, wp, bp, op, N, (int)K, b0, apply_silu, out_stride);          \
     b0 += (BT);                                                                                        \
   }
   while (b0 < B) {
@@ -1584,4 +1589,16 @@ extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void*
   }
 #undef FLUXB_GEMV_LAUNCH
   return launch_status("modulation_gemv");
+}
+
+extern "C" int fluxb_modulation_gemv(const void* vec, const void* w, const void* bias, void* out,
+                                     int64_t B, int64_t N, int64_t K, int apply_silu,
+                                     fluxb_stream_t stream) {
+  return modulation_gemv_impl(vec, w, bias, out, B, N, K, N, apply_silu, false, stream);
+}
+
+extern "C" int fluxb_modulation_gemv_rows(const void* vec, const void* w, const void* bias, void* out,
+                                          int64_t B, int64_t N, int64_t K, int64_t out_stride,
+                                          int apply_silu, int light, fluxb_stream_t stream) {
+  return modulation_gemv_impl(vec, w, bias, out, B, N, K, out_stride, apply_silu, light != 0, stream);
 }

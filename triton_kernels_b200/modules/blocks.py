@@ -14,7 +14,7 @@ triton_kernels/modules/blocks.py:78-172 (and therefore of triton_kernels/flux/la
   linear1 -> split ; GELU ; cat ; linear2        GEMM with a column-split epilogue that writes
                                                    GELU(mlp) next to where attention writes
 
-11 launches per double-stream block (5 per single-stream block) instead of about 40, and no
+13 launches per double-stream block (5 per single-stream block) instead of about 40, and no
 elementwise pass over [L, C] outside a GEMM epilogue.  LayerNorm uses eps 1e-6 like the PyTorch blocks of
 triton_kernels/flux/layers.py:162,165,247 (the reference kernel blocks pass 1e-5; the
 difference is far below bf16 resolution).
@@ -45,7 +45,12 @@ from triton_kernels_b200.kernels.linear import (
 from triton_kernels_b200.kernels.normalization import layer_norm_modulation_into
 from triton_kernels_b200.kernels.positional_embedding import apply_rope
 from triton_kernels_b200.modules.normalization import QKNorm
-from triton_kernels_b200.ops.fused import modulation_silu_linear, qkv_prepare_into, qkv_prepare_scatter
+from triton_kernels_b200.ops.fused import (
+    modulation_silu_linear,
+    modulation_silu_linear_rows,
+    qkv_prepare_into,
+    qkv_prepare_scatter,
+)
 
 LN_EPS = 1e-6
 
@@ -111,6 +116,16 @@ class Modulation(nn.Module):
     def packed(self, vec: Tensor) -> Tensor:
         """[B, multiplier*dim]: shift | scale | gate (| shift2 | scale2 | gate2)."""
         return modulation_silu_linear(vec, self.lin.weight, self.lin.bias)
+
+    def packed_rows(self, vec: Tensor, out: Tensor, first_half: bool, light: bool = False) -> None:
+        """Fills one half of the packed [B, 6*dim] tensor of a double modulation: shift | scale |
+        gate (needed before attention) or shift2 | scale2 | gate2 (needed after it)."""
+        n = self.lin.weight.shape[0] // 2
+        r0, r1 = (0, n) if first_half else (n, 2 * n)
+        bias = self.lin.bias
+        if bias is not None and bias.dtype != torch.bfloat16:
+            bias = bias.to(torch.bfloat16)
+        modulation_silu_linear_rows(vec.contiguous(), self.lin.weight, bias, out, r0, r1, light)
 
     def forward(self, vec: Tensor) -> tuple[ModulationOut, ModulationOut | None]:
         out = self.packed(vec)[:, None, :].chunk(self.multiplier, dim=-1)
@@ -325,6 +340,7 @@ class DoubleStreamBlock(nn.Module):
         # QK norm + RoPE + head-major layout in the qkv GEMM's epilogue when shapes allow (FLUXB_FUSE_QKV=0: off)
         self.fuse_qkv_epilogue = os.environ.get("FLUXB_FUSE_QKV", "1") != "0"
         self._side_stream = None  # created on first use
+        self._mod_stream = None
 
     def forward(self, img: Tensor, txt: Tensor, vec: Tensor, pe: Tensor,
                 modulation: tuple[Tensor, Tensor] | None = None) -> tuple[Tensor, Tensor]:
@@ -349,15 +365,36 @@ class DoubleStreamBlock(nn.Module):
         if self._side_stream is None:
             self._side_stream = torch.cuda.Stream()
         side = self._side_stream
+        # Only shift | scale | gate are needed before attention: the other half of each projection
+        # (56 MB of weights per stream) is launched afterwards in a form that fits on the SMs beside
+        # the q|k|v GEMM and streams its weights while that GEMM computes.
+        split_mod = modulation is None and vec.dtype == torch.bfloat16 and self.img_mod.lin.weight.dtype == torch.bfloat16
+        if split_mod:
+            txt_mod = torch.empty((B, 6 * C), device=dev, dtype=dt)
+            img_mod = torch.empty((B, 6 * C), device=dev, dtype=dt)
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            txt_mod = modulation[0] if modulation is not None else self.txt_mod.packed(vec)
+            if split_mod:
+                self.txt_mod.packed_rows(vec, txt_mod, True)
+            else:
+                txt_mod = modulation[0] if modulation is not None else self.txt_mod.packed(vec)
             h_txt = _ln_mod(txt, txt_mod, 0)
-        img_mod = modulation[1] if modulation is not None else self.img_mod.packed(vec)
+        if split_mod:
+            self.img_mod.packed_rows(vec, img_mod, True)
+        else:
+            img_mod = modulation[1] if modulation is not None else self.img_mod.packed(vec)
         h_img = _ln_mod(img, img_mod, 0)
         main.wait_stream(side)
         for t_ in (txt_mod, h_txt):
             t_.record_stream(main)
+        if split_mod:
+            if self._mod_stream is None:
+                self._mod_stream = torch.cuda.Stream()
+            later = self._mod_stream  # a stream of its own: `side` is needed again before attention
+            later.wait_stream(main)
+            with torch.cuda.stream(later):
+                self.txt_mod.packed_rows(vec, txt_mod, False, light=True)
+                self.img_mod.packed_rows(vec, img_mod, False, light=True)
         mods = (txt_mod, img_mod)  # [B, 6C] each
 
         def gate_of(mod, chunk, b=None):
@@ -445,6 +482,8 @@ class DoubleStreamBlock(nn.Module):
         # MLP: LN+mod2, up-projection with GELU, down-projection with gate/residual
         # (the text stream's LayerNorm is 512 rows, a launch that is all latency: beside the image
         # stream's on the second stream, not before it: 3 us per step)
+        if split_mod:
+            main.wait_stream(self._mod_stream)  # shift2 | scale2 | gate2 are complete
         side.wait_stream(main)
         with torch.cuda.stream(side):
             h2_txt = _ln_mod(x1[0], mods[0], 3)

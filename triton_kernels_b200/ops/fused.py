@@ -86,6 +86,24 @@ def modulation_silu_linear(vec: torch.Tensor, w: torch.Tensor, b: torch.Tensor |
     return out
 
 
+def modulation_silu_linear_rows(vec: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, out: torch.Tensor,
+                                row0: int, row1: int, light: bool = False) -> None:
+    """Columns [row0, row1) of `out` [B, N] = silu(vec) @ w[row0:row1].T + b[row0:row1]: the
+    modulation projection filled in pieces.  `light` launches a form small enough to be resident
+    beside a GEMM, for a piece whose result is needed later."""
+    B, K = vec.shape
+    assert out.shape == (B, w.shape[0]) and out.stride(1) == 1 and 0 <= row0 <= row1 <= w.shape[0]
+    assert vec.is_contiguous() and w.is_contiguous() and vec.dtype == w.dtype == out.dtype == torch.bfloat16
+    bias = None if b is None else b[row0:row1]
+    assert bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous())
+    _lib.check(
+        _lib.load().fluxb_modulation_gemv_rows(
+            _lib.ptr(vec), _lib.ptr(w[row0:row1]), _lib.ptr(bias), _lib.ptr(out[:, row0:row1]), B, row1 - row0, K,
+            out.stride(0), 1, int(light), _lib.stream_handle()
+        )
+    )
+
+
 def qkv_prepare_into(
     streams: list[tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None]],
     pe: torch.Tensor | None,
