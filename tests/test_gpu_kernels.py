@@ -225,6 +225,31 @@ def test_modulation_projection(tk, B, N, K):
     close_bf16(got, want)
 
 
+@pytest.mark.parametrize("B,light", [(1, False), (1, True), (2, True), (3, False)])
+def test_modulation_projection_filled_in_row_ranges(tk, B, light):
+    """The packed [B, 6C] modulation tensor filled by two calls over row ranges (the block computes
+    the half that is needed after attention later, in the light launch form)."""
+    from triton_kernels_b200.ops.fused import modulation_silu_linear_rows
+
+    g = gen(22)
+    K, N = 3072, 6 * 512
+    vec = torch.randn(B, K, generator=g).to(BF)
+    w = (0.02 * torch.randn(N, K, generator=g)).to(BF)
+    b = (0.02 * torch.randn(N, generator=g)).to(BF)
+    out = torch.full((B, N), float("nan"), dtype=BF).cuda()
+    vc, wc, bc = vec.cuda(), w.cuda(), b.cuda()
+    modulation_silu_linear_rows(vc, wc, bc, out, 0, N // 2, False)
+    assert torch.isnan(out[:, N // 2 :].float()).all()  # the other half is untouched
+    modulation_silu_linear_rows(vc, wc, bc, out, N // 2, N, light)
+    close_bf16(out, O.linear(O.silu(vec.float()), w.float(), b.float()))
+    # a ragged range in the light form
+    out2 = torch.zeros((B, N), dtype=BF).cuda()
+    modulation_silu_linear_rows(vc, wc, bc, out2, 5, 1006, True)
+    want = O.linear(O.silu(vec.float()), w.float(), b.float())
+    close_bf16(out2[:, 5:1006], want[:, 5:1006])
+    assert float(out2[:, :5].abs().max()) == 0 and float(out2[:, 1006:].abs().max()) == 0
+
+
 # ------------------------------------------------------------------ linear (tcgen05 GEMM)
 @pytest.mark.parametrize(
     "M,K,N,act,bias",
