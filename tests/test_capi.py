@@ -65,6 +65,11 @@ def test_argument_validation_needs_no_gpu(lib):
     assert rc == _lib.ERR_UNSUPPORTED
     assert lib.fluxb_silu(None, None, 0, _lib.BF16, None) == 0  # empty input is a no-op
     assert lib.fluxb_rms_norm_bwd_partial_rows(1000) == 16
+    # modulation projection over a row range: the output row stride cannot be shorter than the range
+    rc = lib.fluxb_modulation_gemv_rows(None, None, None, None, 1, 512, 3072, 256, 1, 0, None)
+    assert rc == _lib.ERR_BAD_ARG
+    assert lib.fluxb_modulation_gemv_rows(None, None, None, None, 1, 0, 3072, 0, 1, 1, None) == 0  # empty range
+    assert lib.fluxb_layer_norm_modulation(None, None, None, None, 0, 3072, 16, 3072, 3072, 0, 1e-6, _lib.BF16, None) == 0
 
 
 def test_python_wrappers_reject_cpu_tensors():
