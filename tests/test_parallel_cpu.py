@@ -153,3 +153,18 @@ def test_key_split_estimate_picks_only_part_filled_last_waves():
     assert key_splits_for(1, 24, 4608, 4608, 128, 148) == 1
     assert key_splits_for(2, 4, 512, 512, 128, 148) == 1  # fewer than eight key tiles: never
     assert key_splits_for(1, 2, 20480, 20480, 128, 148) == 2
+
+
+def test_exchange_pieces_are_whole_gemm_tiles():
+    from triton_kernels_b200.parallel.ulysses import exchange_pieces
+
+    for rows in (512, 1024, 2048, 4096, 8192, 9984, 600, 257):
+        pieces = exchange_pieces(rows, 2)
+        assert pieces[0][0] == 0 and pieces[-1][1] == rows
+        assert all(a1 == b0 for (_, a1), (b0, _) in zip(pieces[:-1], pieces[1:]))  # contiguous, in order
+        assert all((b - a) % 256 == 0 for a, b in pieces[:-1])  # only the last piece may be ragged
+        assert len(pieces) <= 2 and all(b > a for a, b in pieces)
+    assert exchange_pieces(2048, 2) == [(0, 1024), (1024, 2048)]
+    assert exchange_pieces(9984, 2) == [(0, 5120), (5120, 9984)]
+    assert exchange_pieces(256, 2) == [(0, 256)]
+    assert exchange_pieces(4096, 4) == [(0, 1024), (1024, 2048), (2048, 3072), (3072, 4096)]

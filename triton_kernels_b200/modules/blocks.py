@@ -429,20 +429,17 @@ class DoubleStreamBlock(nn.Module):
             # one piece's stores into the peers' arenas (NVLink-bound, few issue slots) run beside
             # the next piece's projection instead of after the whole projection
             pb = sp.peer_buffers(B, Lt + Li, H, D, dt)
-            n_chunks = 2  # three and four pieces measured slower than two (1.83 / 1.85 against 1.81 ms on four GPUs)
-            rows = (Li // n_chunks + 255) // 256 * 256  # whole 256-row GEMM tiles per piece
-            cuts = [min(i * rows, Li) for i in range(n_chunks + 1)]
-            cuts[-1] = Li
+            from triton_kernels_b200.parallel.ulysses import exchange_pieces
+
+            # two pieces: three and four measured slower (1.83 / 1.85 against 1.81 ms on four GPUs)
+            pieces = exchange_pieces(Li, 2)
             qkvs = [torch.empty((B, L, 3 * C), device=dev, dtype=dt) for L in Ls]
             x_img, y_img = h1[1].view(Li, C), qkvs[1].view(Li, 3 * C)
             a_t, a_i = attns
             norms = [(a.norm.query_norm.scale.to(dt), a.norm.key_norm.scale.to(dt)) for a in attns]
             pe_rows = pe.reshape(-1, D // 2, 2, 2)
             scat = (pb.P, pb.k_off, pb.v_off, H, D, pb.qkv_strides)
-            for i in range(n_chunks):
-                r0, r1 = cuts[i], cuts[i + 1]
-                if r1 <= r0:
-                    continue
+            for i, (r0, r1) in enumerate(pieces):
                 last = r1 == Li
                 probs = [dict(x2d=x_img[r0:r1], w=a_i.qkv.weight, b=a_i.qkv.bias, y=y_img[r0:r1])]
                 if i == 0:

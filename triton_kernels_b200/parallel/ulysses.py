@@ -191,6 +191,16 @@ class _PeerBuffers:
         return self._q_bases_from[row]
 
 
+def exchange_pieces(rows: int, pieces: int = 2, tile: int = 256) -> list[tuple[int, int]]:
+    """Row ranges in which the pipelined peer exchange projects and scatters `rows` image tokens:
+    `pieces` ranges of equal size rounded up to whole GEMM row tiles (so that cutting the
+    projection does not add a partial tile), the last one taking what is left; empty ranges are
+    dropped."""
+    per = (rows // pieces + tile - 1) // tile * tile
+    cuts = [min(i * per, rows) for i in range(pieces)] + [rows]
+    return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+
+
 def shard_joint_sequence(txt: Tensor, img: Tensor, pe: Tensor, rank: int, world: int):
     """This rank's slice of both streams and the matching rows of the RoPE table.
 
